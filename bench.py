@@ -1,0 +1,379 @@
+"""Benchmark of the quantised-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--workload NAME] [--impl reference]
+
+Default workload: one decode step of the Llama-3-70B-shaped FP8 (e4m3, per-channel
+scale) linear stack, tensor-parallel over N GPUs of one node (column-parallel QKV /
+gate+up / LM head, row-parallel O / down followed by an NCCL all-reduce), random-init
+weights generated on the device from a seed, bf16 activations ~ N(0,1).  A "step" is
+one pass of all 321 linears for a batch of B tokens; `value` is tokens/s of the whole
+job with inputs resident in HBM; `e2e` is the same step driven through the host entry
+point (pinned host input -> H2D -> step -> D2H of the logits).  The roofline object is
+the decode matvec kernel: algorithmic bytes of a step's matvec launches over their
+device time, against the measured HBM copy bandwidth.  No model checkpoint or dataset
+is involved: the shapes are the only thing taken from the named model.
+
+One process per GPU: for N > 1 launch with
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 ... bench.py --gpus N
+(torch.distributed over gloo carries only the NCCL id, barriers and the max-over-ranks
+reduction of the timings; all device work goes through libullm_cuda).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "ullm-project_b200"), os.path.join(ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+SEED = 20260803
+WORKLOADS = {
+    # name: (shape attr, encoding name, description)
+    "stack70b-fp8": ("LLAMA3_70B", "fp8", "Llama-3-70B-shaped FP8 e4m3 linear stack, one decode step"),
+    "stack8b-aq4": ("LLAMA3_8B", "aq4", "Llama-3-8B-shaped AQ4 linear stack, one decode step"),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def stack_algorithmic_bytes(shape, enc, batch, tp):
+    """Per rank and per step: packed weights + scales + activations read and written by the linears."""
+    qd, kvd = shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
+    per = (lambda n, k: n * k // 2 + n * k // 64) if enc == "aq4" else (lambda n, k: n * k + 4 * n)
+    lin = [((qd + 2 * kvd) // tp, shape.hidden, 2, 2), (shape.hidden, qd // tp, 2, 4),
+           (2 * shape.ffn // tp, shape.hidden, 4, 2), (shape.hidden, shape.ffn // tp, 2, 4)]
+    w = shape.layers * sum(per(n, k) for n, k, _, _ in lin) + per(shape.vocab // tp, shape.hidden)
+    a = shape.layers * sum(batch * (k * xi + n * yo) for n, k, xi, yo in lin)
+    a += shape.layers * batch * shape.ffn // tp * 2  # the SwiGLU prologue reads gate and up
+    a += batch * (shape.hidden * 4 + shape.vocab // tp * 2)
+    return w, a
+
+
+def cpu_sample(shape, enc, batch, seconds_hint=15.0):
+    """Times the plain-C port on ONE decoder layer (QKV, O, gate+up, down) of the same widths
+    with all host threads and scales to the whole stack by weight elements."""
+    import oracle_c as oc
+
+    rng = np.random.default_rng(SEED)
+    qd, kvd = shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
+    lin = [(qd + 2 * kvd, shape.hidden), (shape.hidden, qd), (2 * shape.ffn, shape.hidden), (shape.hidden, shape.ffn)]
+    mats = []
+    for n, k in lin:
+        x = oc.synth_activations_bits(SEED, 5000 + k, batch, k)
+        if enc == "aq4":
+            mats.append((x, rng.integers(0x11, 0xFF, (n, k // 2), dtype=np.uint8),
+                         np.full((n, k // 128), 0.003, np.float16)))
+        else:
+            codes = rng.integers(0, 0x7E, (n, k), dtype=np.uint8) | (rng.integers(0, 2, (n, k), dtype=np.uint8) << 7)
+            mats.append((x, codes, np.full(n, 1e-4, np.float32)))
+    elems = sum(n * k for n, k in lin)
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for x, v, s in mats:
+            (oc.linear_aq4 if enc == "aq4" else oc.linear_fp8)(x, v, s)
+        return time.perf_counter() - t0
+
+    return one_pass, elems, oc.num_threads()
+
+
+def run_reference(args, shape, enc):
+    """The reference project has no CPU (or any) implementation of this path, so the
+    reference arm times this repository's plain-C port of the format spec on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    one_pass, elems, threads = cpu_sample(shape, enc, args.batch)
+    for _ in range(args.warmup):
+        one_pass()
+    times = [one_pass() for _ in range(args.steps)]
+    t = sum(times) / len(times)
+    scale = shape.weight_elements() / elems
+    value = args.batch / (t * scale)
+    sample = (f"one decoder layer (QKV, O, gate+up, down; {elems} weight elements) of the same widths per step, "
+              f"scaled x{scale:.2f} to the whole stack by weight elements")
+    line = {
+        "impl": "reference", "metric": "linear-stack decode tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * scale * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOADS[args.workload][2] + f", batch {args.batch}", "batch": args.batch,
+                   "encoding": enc, "note": "CPU port of the spec (the reference has no implementation of this path)"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps):
+    """Time per launch of one matvec shape over enough distinct weight copies to exceed 2x L2,
+    replayed as one graph (so the figure is HBM, not L2, and launch gaps are the graph's)."""
+    vb, sb = U.weight_bytes(enc_id, n, k)
+    copies = max(2, int(2 * 130e6 // (vb + sb)) + 1)
+    src = ctx.alloc(n * k * 4)
+    q.synth_weights(SEED, 4242, 0, n * k, 0.02, src.at(0))
+    bufs, descs = [], []
+    xb, yb = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+    q.synth_activations(SEED, 4243, 0, m * k, xb.at(0))
+    for _ in range(copies):
+        v, s = ctx.alloc(vb), ctx.alloc(sb)
+        wd = U.weight_desc(enc_id, n, k, v.at(0), s.at(0))
+        q.quantize(src.at(0), wd)
+        bufs += [v, s]
+        descs.append(U.linear_desc(wd, m, xb.at(0), yb.at(0), kernel=U.KERNEL_MATVEC))
+    q.capture_begin()
+    for d in descs:
+        q.linear_enqueue(d)
+    g = q.capture_end()
+    for _ in range(3):
+        g.launch(q)
+    q.synchronize()
+    a = q.signal()
+    for _ in range(reps):
+        g.launch(q)
+    b = q.signal()
+    b.query(600000)
+    ms = b.elapsed_ms_since(a)
+    a.close()
+    b.close()
+    g.close()
+    for buf in bufs + [src, xb, yb]:
+        buf.close()
+    us = ms * 1e3 / (reps * copies)
+    algo = vb + sb + m * k * 2 + m * n * 2
+    return {"us_per_launch": us, "algorithmic_bytes": algo, "gbs": algo / us / 1e3, "weight_copies": copies}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; the line says so)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the single-matvec figures and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    import ullm_cuda as U
+
+    shape_name, enc, descr = WORKLOADS[args.workload]
+    shape = getattr(U, shape_name)
+    if args.layers:
+        shape = U.StackShape(args.layers, shape.hidden, shape.q_heads, shape.kv_heads, shape.head_dim, shape.ffn, shape.vocab)
+    if args.impl == "reference":
+        run_reference(args, shape, enc)
+        return
+    enc_id = U.ENCODING_AQ4 if enc == "aq4" else U.ENCODING_FP8_CHANNEL
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch one process per GPU with torch.distributed.run")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # plumbing only: NCCL id, barrier, max over ranks
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    probe = U.backend_probe()
+    if not probe.available:
+        raise SystemExit(f"no usable B200: {probe.diagnostic} (there is no CPU fallback to measure)")
+    ctx = U.Context(local)
+    q = ctx.queue()
+    comm = None
+    if world > 1:
+        box = [U.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = U.Comm(ctx, box[0], rank, world)
+
+    B = args.batch
+    stack = U.Stack(ctx, q, shape, enc_id, max_tokens=B, seed=SEED, tp_rank=rank, tp_size=world, comm=comm)
+    xin = ctx.alloc(B * shape.hidden * 2)
+    yout = ctx.alloc(B * stack.local_vocab * 2)
+    q.synth_activations(SEED, 77, 0, B * shape.hidden, xin.at(0))
+    q.synchronize()
+
+    def barrier():
+        q.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing: W warm-up steps, then exactly K steps between two events -------
+    for _ in range(args.warmup):
+        stack.step(B, xin.at(0), yout.at(0))
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    a = q.signal()
+    for _ in range(args.steps):
+        stack.step(B, xin.at(0), yout.at(0))
+    b = q.signal()
+    b.query(3600000)
+    ms_total = b.elapsed_ms_since(a)
+    a.close()
+    b.close()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = max_over_ranks(ms_total)
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the host entry point: pinned H2D + step + D2H every step ----------
+    x_host = q.download(xin.at(0), (B, shape.hidden), np.uint16)
+    y_host = np.empty((B, stack.local_vocab), np.uint16)
+    for _ in range(args.warmup):
+        stack.step_host_into(x_host, y_host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        stack.step_host_into(x_host, y_host)
+    q.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+
+    wbytes, launches = stack.stats()
+    w_algo, a_algo = stack_algorithmic_bytes(shape, enc, B, world)
+    assert w_algo == wbytes, (w_algo, wbytes)
+    peak, peak_src = peaks()
+
+    line = None
+    if rank == 0:
+        n_matvec = 4 * shape.layers + 1
+        achieved = (w_algo + a_algo) / (ms_step * 1e-3) / 1e9  # GB/s per GPU over the whole step
+        line = {
+            "metric": "linear-stack decode tokens/s", "value": B / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 accumulate over e4m3 weights and bf16 activations" if enc == "fp8"
+            else "f32 accumulate over 4-bit weights (fp16 group scales) and bf16 activations",
+            "data": "synthetic",
+            "config": {"workload": f"{descr}, batch {B}, tensor-parallel over {world} GPU(s)", "batch": B,
+                       "encoding": enc, "layers": shape.layers, "hidden": shape.hidden, "ffn": shape.ffn,
+                       "vocab": shape.vocab, "parallelism": f"tp{world}",
+                       "l2": "weights streamed per step exceed L2 many times over (no flush needed)",
+                       "layers_overridden": bool(args.layers)},
+            "e2e": {"value": B * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": B * shape.hidden * 2,
+                    "d2h_bytes_per_step": B * stack.local_vocab * 2, "ms_per_step": e2e_s / args.steps * 1e3},
+            "gpu_launches": launches * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": f"matvec_kernel ({n_matvec} launches per step"
+                                   + (f" + {2 * shape.layers} all-reduces" if world > 1 else "") + ")",
+                         "algorithmic_bytes_per_step": w_algo + a_algo,
+                         "note": "achieved = per-GPU algorithmic bytes of one step / device time of one step"},
+        }
+
+    # ---- explanatory figures (rank 0, N = 1 only): single matvec shapes and the CPU port ----------
+    stack.close()
+    xin.close()
+    yout.close()
+    if rank == 0 and world == 1 and not args.no_extra:
+        extra = {}
+        for name, e, n, k, m in (("aq4_m1_k4096_n4096", U.ENCODING_AQ4, 4096, 4096, 1),
+                                 ("fp8_m1_k4096_n14336", U.ENCODING_FP8_CHANNEL, 14336, 4096, 1),
+                                 ("fp8_m4_k4096_n14336", U.ENCODING_FP8_CHANNEL, 14336, 4096, 4),
+                                 ("fp8_m8_k4096_n14336", U.ENCODING_FP8_CHANNEL, 14336, 4096, 8),
+                                 ("fp8_m1_k8192_n57344", U.ENCODING_FP8_CHANNEL, 57344, 8192, 1),
+                                 ("aq4_m1_k4096_n28672", U.ENCODING_AQ4, 28672, 4096, 1)):
+            r = time_matvec_extra(U, ctx, q, e, n, k, m, reps=20)
+            r["frac_of_peak"] = r["gbs"] / peak
+            extra[name] = r
+        line["matvec"] = extra
+        one_pass, elems, threads = cpu_sample(shape, enc, B)
+        one_pass()
+        t = min(one_pass() for _ in range(2))
+        scale = shape.weight_elements() / elems
+        line["cpu_baseline"] = {
+            "value": B / (t * scale), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"one decoder layer of the same widths ({elems} weight elements, {t:.2f} s with {threads} "
+                      f"threads), scaled x{scale:.1f} to the whole stack by weight elements"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if comm is not None:
+        comm.close()
+    q.close()
+    ctx.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

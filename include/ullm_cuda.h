@@ -1,0 +1,406 @@
+/* ullm_cuda.h — versioned C ABI of the CUDA (sm_100a) quantised-linear backend.
+ *
+ * This is the CUDA sibling of the reference's HIP boundary and keeps its
+ * conventions (reference file:line given beside each group):
+ *   - every function returns ullm_status_t and never throws across the boundary;
+ *   - the caller owns an optional error sink; message_length is always the
+ *     untruncated length and a truncated message turns the return value into
+ *     ULLM_STATUS_BUFFER_TOO_SMALL (include/ullm/hip.h:48-63);
+ *   - validation order is: sink, then the versioned struct, then arguments
+ *     (native/hip/src/hip_stub.cpp:43-118);
+ *   - extensible structs start with struct_size + abi_version and end with
+ *     reserved words that must be zero;
+ *   - handles are opaque and never dereferenced by callers (hip.h:40-46);
+ *   - host data is copied during the call; the library keeps no pointer into
+ *     caller memory after return (native/hip/src/hip_evidence_runtime.hip.cpp:618-620);
+ *   - completion = submit -> wait(timeout_ms) -> destroy; wait polls, it never
+ *     blocks without a deadline; a completion is consumed by wait
+ *     (native/hip/src/evidence_abi.h:48-59, hip_evidence_runtime.hip.cpp:508-535, :691-698);
+ *   - there is no CPU fallback: without a usable sm_100 device every compute
+ *     entry returns ULLM_STATUS_CUDA_UNAVAILABLE
+ *     (native/hip/src/hip_evidence_stub.cpp:103-127).
+ * The header is self-contained C99 / C++11.
+ */
+#ifndef ULLM_CUDA_H
+#define ULLM_CUDA_H
+
+#include <stdint.h>
+
+/* export marker, the counterpart of ULLM_HIP_API (include/ullm/hip.h:6-14) */
+#if defined(__GNUC__)
+#define ULLM_CUDA_API __attribute__((visibility("default")))
+#else
+#define ULLM_CUDA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ULLM_CUDA_ABI_VERSION UINT32_C(1)
+#define ULLM_CUDA_LIBRARY_VERSION_MAJOR UINT32_C(0)
+#define ULLM_CUDA_LIBRARY_VERSION_MINOR UINT32_C(1)
+#define ULLM_CUDA_LIBRARY_VERSION_PATCH UINT32_C(0)
+
+/* ---- status codes: 0-7 are the reference's public codes (hip.h:21-30), 8-12 its
+ * private evidence codes (evidence_abi.h:13-17); 13+ are new. ------------------- */
+#ifndef ULLM_STATUS_OK
+typedef uint32_t ullm_status_t;
+#define ULLM_STATUS_OK UINT32_C(0)
+#define ULLM_STATUS_INVALID_ARGUMENT UINT32_C(1)
+#define ULLM_STATUS_BUFFER_TOO_SMALL UINT32_C(2)
+#define ULLM_STATUS_UNSUPPORTED UINT32_C(3)
+#define ULLM_STATUS_INVALID_ABI_VERSION UINT32_C(5)
+#define ULLM_STATUS_RESERVED_NONZERO UINT32_C(6)
+#define ULLM_STATUS_INTERNAL_ERROR UINT32_C(7)
+#endif
+#define ULLM_STATUS_CUDA_UNAVAILABLE UINT32_C(4) /* same slot as ULLM_STATUS_HIP_UNAVAILABLE */
+#define ULLM_STATUS_CUDA_TIMEOUT UINT32_C(8)
+#define ULLM_STATUS_CUDA_INVALID_HANDLE UINT32_C(9)
+#define ULLM_STATUS_CUDA_ZERO_DISPATCH UINT32_C(10)
+#define ULLM_STATUS_CUDA_RUNTIME_ERROR UINT32_C(11)
+#define ULLM_STATUS_CUDA_DISPATCH_CONTRACT UINT32_C(12)
+#define ULLM_STATUS_CUDA_OUT_OF_MEMORY UINT32_C(13)
+#define ULLM_STATUS_CUDA_OUT_OF_RANGE UINT32_C(14)   /* a tensor span leaves its buffer */
+#define ULLM_STATUS_CUDA_COMM_ERROR UINT32_C(15)     /* NCCL missing or failed */
+#define ULLM_STATUS_CUDA_DEVICE_FLAGGED UINT32_C(16) /* a kernel gave up a bounded wait */
+
+#define ULLM_BACKEND_CUDA UINT32_C(2) /* next id after ULLM_BACKEND_HIP = 1 (hip.h:32) */
+
+/* physical scalar types, numbered like ullm-core's DType (crates/ullm-core/src/dtype.rs:6-16) */
+#define ULLM_CUDA_DTYPE_BF16 UINT32_C(0)
+#define ULLM_CUDA_DTYPE_F16 UINT32_C(1)
+#define ULLM_CUDA_DTYPE_F32 UINT32_C(2)
+#define ULLM_CUDA_DTYPE_F8E4M3FN UINT32_C(3)
+#define ULLM_CUDA_DTYPE_I8 UINT32_C(7)
+#define ULLM_CUDA_DTYPE_U8 UINT32_C(8)
+
+/* storage encodings, the additive siblings of Encoding::Nvfp4 (dtype.rs:56-66) */
+#define ULLM_CUDA_ENCODING_UNQUANTIZED UINT32_C(0)
+#define ULLM_CUDA_ENCODING_NVFP4 UINT32_C(1) /* descriptor only: every op answers UNSUPPORTED */
+#define ULLM_CUDA_ENCODING_AQ4 UINT32_C(2)   /* u8 [N,K/2] nibbles + f16 [N,K/group] scales */
+#define ULLM_CUDA_ENCODING_FP8_CHANNEL UINT32_C(3) /* e4m3fn [N,K] + f32 [N] scales */
+
+#define ULLM_CUDA_AQ4_GROUP UINT32_C(128)
+
+/* opaque handles (hip.h:40-46) */
+typedef struct ullm_cuda_context_t ullm_cuda_context_t;
+typedef struct ullm_cuda_queue_t ullm_cuda_queue_t;
+typedef struct ullm_cuda_buffer_t ullm_cuda_buffer_t;
+typedef struct ullm_cuda_completion_t ullm_cuda_completion_t;
+typedef struct ullm_cuda_graph_t ullm_cuda_graph_t;
+typedef struct ullm_cuda_comm_t ullm_cuda_comm_t;
+typedef struct ullm_cuda_stack_t ullm_cuda_stack_t;
+
+/* identical layout to ullm_error_sink_t (hip.h:48-55): 48 bytes, align 8 */
+typedef struct ullm_cuda_error_sink_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  char *message;
+  uint64_t message_capacity; /* includes the NUL */
+  uint64_t message_length;   /* required length without the NUL, even when truncated */
+  uint64_t reserved[2];
+} ullm_cuda_error_sink_t;
+
+typedef struct ullm_cuda_version_info_t { /* hip.h:76-83 */
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t major;
+  uint32_t minor;
+  uint32_t patch;
+  uint32_t reserved[3];
+} ullm_cuda_version_info_t;
+
+typedef struct ullm_cuda_backend_probe_result_t { /* hip.h:85-92, extended */
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t backend;
+  uint32_t available;            /* 1 when at least one sm_100 device is usable */
+  uint32_t cuda_runtime_present; /* 1 when the CUDA runtime answered at all */
+  uint32_t device_count;
+  uint32_t sm_major; /* of device 0 */
+  uint32_t sm_minor;
+  uint32_t sm_count;
+  uint32_t l2_bytes_mib;
+  uint64_t global_memory_bytes;
+  uint32_t reserved[4];
+} ullm_cuda_backend_probe_result_t;
+
+typedef struct ullm_cuda_context_probe_result_t { /* hip.h:94-100 */
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t context_present;
+  uint32_t cuda_available;
+  uint32_t device_ordinal;
+  uint32_t reserved[3];
+} ullm_cuda_context_probe_result_t;
+
+/* A span inside a device buffer.  Every op checks offset + bytes against the
+ * buffer size on the host before launching anything. */
+typedef struct ullm_cuda_tensor_t {
+  ullm_cuda_buffer_t *buffer;
+  uint64_t offset_bytes;
+} ullm_cuda_tensor_t;
+
+/* A quantised weight W[N,K] (row n = output channel, K contiguous). */
+typedef struct ullm_cuda_weight_t {
+  uint32_t encoding;   /* ULLM_CUDA_ENCODING_AQ4 | ULLM_CUDA_ENCODING_FP8_CHANNEL */
+  uint32_t group_size; /* 128 for AQ4; 0 for FP8_CHANNEL */
+  uint64_t n;
+  uint64_t k;
+  ullm_cuda_tensor_t values; /* AQ4: u8 [N,K/2]; FP8: e4m3fn [N,K] */
+  ullm_cuda_tensor_t scales; /* AQ4: f16 [N,K/group]; FP8: f32 [N] */
+} ullm_cuda_weight_t;
+
+/* ---- version / probe: the CUDA counterparts of hip.h:106-121 ---------------- */
+ULLM_CUDA_API ullm_status_t ullm_cuda_get_abi_version(uint32_t *abi_version, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_query_version(ullm_cuda_version_info_t *version, ullm_cuda_error_sink_t *error_sink);
+/* ULLM_STATUS_OK with available=1 on a usable sm_100 device; ULLM_STATUS_CUDA_UNAVAILABLE
+ * (result still filled) otherwise; ULLM_STATUS_UNSUPPORTED for any other backend id. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_backend_probe(uint32_t backend, ullm_cuda_backend_probe_result_t *result,
+                                      ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_context_probe(const ullm_cuda_context_t *context,
+                                      ullm_cuda_context_probe_result_t *result,
+                                      ullm_cuda_error_sink_t *error_sink);
+
+/* ---- context / queue / buffer / completion.  Replaces the per-request stream,
+ * event and buffer lifecycle of native/hip/src/hip_evidence_runtime.hip.cpp:53-71,
+ * :585-659 with objects that are created once and reused. ---------------------- */
+ULLM_CUDA_API ullm_status_t ullm_cuda_context_create(uint32_t device_ordinal, ullm_cuda_context_t **context,
+                                       ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_context_destroy(ullm_cuda_context_t **context, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_queue_create(ullm_cuda_context_t *context, ullm_cuda_queue_t **queue,
+                                     ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_queue_destroy(ullm_cuda_queue_t **queue, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_alloc(ullm_cuda_context_t *context, uint64_t size_bytes,
+                                     ullm_cuda_buffer_t **buffer, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_free(ullm_cuda_buffer_t **buffer, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_size(const ullm_cuda_buffer_t *buffer, uint64_t *size_bytes,
+                                    ullm_cuda_error_sink_t *error_sink);
+/* Synchronous with respect to the caller: the bytes have left / reached host
+ * memory when the call returns; ordered after earlier work on the queue. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_upload(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t dst, const void *host_src,
+                                      uint64_t size_bytes, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_download(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t src, void *host_dst,
+                                        uint64_t size_bytes, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_fill(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t dst, uint8_t value,
+                                    uint64_t size_bytes, ullm_cuda_error_sink_t *error_sink);
+/* Records a completion point on the queue (an event with timing).  The handle
+ * is consumed by ullm_cuda_completion_wait unless that call times out. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_queue_signal(ullm_cuda_queue_t *queue, ullm_cuda_completion_t **completion,
+                                     ullm_cuda_error_sink_t *error_sink);
+
+typedef struct ullm_cuda_completion_result_t { /* evidence_abi.h:27-40 */
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint64_t dispatch_count; /* kernels launched on the queue since the previous signal */
+  uint64_t copy_count;     /* cudaMemcpyAsync transfers since the previous signal */
+  uint32_t selected_backend; /* always ULLM_BACKEND_CUDA */
+  uint32_t fallback_used;    /* always 0 */
+  uint32_t terminal;
+  uint32_t device_flags; /* non-zero when a kernel recorded a bounded-wait expiry */
+  uint32_t reserved[4];
+} ullm_cuda_completion_result_t;
+
+/* timeout_ms == 0 is a single poll (hip_evidence_runtime.hip.cpp:508-535).
+ * On ULLM_STATUS_CUDA_TIMEOUT the handle stays valid; on every other outcome it
+ * is consumed and a later use returns ULLM_STATUS_CUDA_INVALID_HANDLE. result may be NULL. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint32_t timeout_ms,
+                                        ullm_cuda_completion_result_t *result,
+                                        ullm_cuda_error_sink_t *error_sink);
+/* Milliseconds of device time between two completions that have both been
+ * reached (the handles stay valid: use this BEFORE waiting consumes them, or
+ * wait with a timeout that keeps them — see ullm_cuda_completion_query). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_completion_elapsed_ms(ullm_cuda_completion_t *start, ullm_cuda_completion_t *end,
+                                              float *milliseconds, ullm_cuda_error_sink_t *error_sink);
+/* Poll without consuming: OK when reached, ULLM_STATUS_CUDA_TIMEOUT when not. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_completion_query(ullm_cuda_completion_t *completion, uint32_t timeout_ms,
+                                         ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_completion_destroy(ullm_cuda_completion_t **completion,
+                                           ullm_cuda_error_sink_t *error_sink);
+
+/* Stream capture into a replayable graph: everything enqueued on the queue
+ * between begin and end is recorded instead of run. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_queue_capture_begin(ullm_cuda_queue_t *queue, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_queue_capture_end(ullm_cuda_queue_t *queue, ullm_cuda_graph_t **graph,
+                                          ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_graph_launch(ullm_cuda_graph_t *graph, ullm_cuda_queue_t *queue,
+                                     ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_graph_destroy(ullm_cuda_graph_t **graph, ullm_cuda_error_sink_t *error_sink);
+
+/* ---- synthetic data (counter-based, bit-identical to the CPU oracle) ---------- */
+/* fp32 out[i] = std * z(seed, tensor_id, first_element + i) */
+ULLM_CUDA_API ullm_status_t ullm_cuda_synth_weights(ullm_cuda_queue_t *queue, uint64_t seed, uint64_t tensor_id,
+                                      uint64_t first_element, uint64_t count, float std,
+                                      ullm_cuda_tensor_t out_f32, ullm_cuda_error_sink_t *error_sink);
+/* bf16 out[i] = bf16_rne(z(...)) */
+ULLM_CUDA_API ullm_status_t ullm_cuda_synth_activations(ullm_cuda_queue_t *queue, uint64_t seed, uint64_t tensor_id,
+                                          uint64_t first_element, uint64_t count, ullm_cuda_tensor_t out_bf16,
+                                          ullm_cuda_error_sink_t *error_sink);
+
+/* ---- quantisation, packing, unpacking (bit-exact against the oracle).  The
+ * reference has no counterpart: these fill the encodings that
+ * crates/ullm-core/src/dtype.rs:56-122 only describes. -------------------------- */
+/* fp32 W[N,K] -> weight.values / weight.scales.  K % group == 0, else UNSUPPORTED. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_quantize(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t src_f32,
+                                 const ullm_cuda_weight_t *weight, ullm_cuda_error_sink_t *error_sink);
+/* AQ4 only: nibbles -> int8 q[N,K] in [-8,7]. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_aq4_unpack(ullm_cuda_queue_t *queue, const ullm_cuda_weight_t *weight,
+                                   ullm_cuda_tensor_t out_i8, ullm_cuda_error_sink_t *error_sink);
+/* AQ4 only: int8 q[N,K] -> nibbles (scales untouched). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_aq4_pack(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t src_i8,
+                                 const ullm_cuda_weight_t *weight, ullm_cuda_error_sink_t *error_sink);
+/* W'[N,K] as out_dtype (F32 exact; BF16 rounds to nearest even). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_dequantize(ullm_cuda_queue_t *queue, const ullm_cuda_weight_t *weight,
+                                   ullm_cuda_tensor_t out, uint32_t out_dtype,
+                                   ullm_cuda_error_sink_t *error_sink);
+
+/* ---- the linear op: y[M,N] = prologue(x)[M,K] . W'[N,K]^T, fp32 accumulate ------ */
+#define ULLM_CUDA_PROLOGUE_NONE UINT32_C(0)
+#define ULLM_CUDA_PROLOGUE_RMSNORM UINT32_C(1) /* x <- bf16(x * rsqrt(mean(x^2) + eps)), weight-free */
+#define ULLM_CUDA_PROLOGUE_SWIGLU UINT32_C(2)  /* input is [M,2K] (gate | up); x <- bf16(silu(gate) * up) */
+
+#define ULLM_CUDA_KERNEL_AUTO UINT32_C(0)
+#define ULLM_CUDA_KERNEL_MATVEC UINT32_C(1) /* CUDA-core streaming kernel, M <= 8 */
+#define ULLM_CUDA_KERNEL_GEMM UINT32_C(2)   /* tcgen05 / TMEM kernel */
+
+typedef struct ullm_cuda_linear_desc_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  ullm_cuda_weight_t weight;
+  uint64_t m;
+  ullm_cuda_tensor_t input;
+  uint64_t input_row_stride; /* elements; 0 = dense */
+  ullm_cuda_tensor_t output;
+  uint64_t output_row_stride; /* elements; 0 = dense (N) */
+  uint32_t input_dtype;       /* BF16, or F32 (rounded to bf16 on load) */
+  uint32_t output_dtype;      /* BF16 or F32 */
+  uint32_t prologue;
+  uint32_t kernel;
+  float rms_eps;
+  uint32_t reserved[5];
+} ullm_cuda_linear_desc_t;
+
+/* Answers without touching the device: OK, UNSUPPORTED (with a reason in the
+ * sink) or an argument error.  Mirrors Backend::supports (crates/ullm-core/src/backend.rs:8). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_supports(const ullm_cuda_linear_desc_t *desc, uint32_t *selected_kernel,
+                                        ullm_cuda_error_sink_t *error_sink);
+/* Enqueue only (ordering by the queue; use ullm_cuda_queue_signal to observe completion). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                       ullm_cuda_error_sink_t *error_sink);
+/* Enqueue + signal in one call: the submit -> wait -> destroy shape of evidence_abi.h:48-59. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                      ullm_cuda_completion_t **completion,
+                                      ullm_cuda_error_sink_t *error_sink);
+
+/* ---- tensor-parallel communicator (NCCL, loaded at run time) ------------------- */
+#define ULLM_CUDA_COMM_ID_BYTES 128
+ULLM_CUDA_API ullm_status_t ullm_cuda_comm_unique_id(uint8_t id[ULLM_CUDA_COMM_ID_BYTES], ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_comm_create(ullm_cuda_context_t *context, const uint8_t id[ULLM_CUDA_COMM_ID_BYTES],
+                                    uint32_t rank, uint32_t size, ullm_cuda_comm_t **comm,
+                                    ullm_cuda_error_sink_t *error_sink);
+/* in-place sum over ranks; dtype F32 or BF16 */
+ULLM_CUDA_API ullm_status_t ullm_cuda_comm_all_reduce(ullm_cuda_comm_t *comm, ullm_cuda_queue_t *queue,
+                                        ullm_cuda_tensor_t data, uint64_t count, uint32_t dtype,
+                                        ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_comm_destroy(ullm_cuda_comm_t **comm, ullm_cuda_error_sink_t *error_sink);
+
+/* ---- linear stack of a decoder: per layer QKV, O, gate+up, down; then the LM head.
+ * Weights are generated on the device from the seed and quantised in place.
+ * tp_size > 1: QKV, gate+up and the LM head are column-parallel (this rank holds
+ * its slice of N), O and down are row-parallel (this rank holds its slice of K)
+ * followed by a sum over ranks. ------------------------------------------------- */
+typedef struct ullm_cuda_stack_desc_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t encoding; /* AQ4 or FP8_CHANNEL */
+  uint32_t layers;
+  uint32_t hidden;
+  uint32_t q_heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t ffn;
+  uint32_t vocab;
+  uint32_t tp_rank;
+  uint32_t tp_size;
+  uint32_t max_tokens; /* largest M of one step */
+  uint32_t flags;
+  uint64_t seed;
+  float rms_eps;
+  uint32_t reserved[5];
+} ullm_cuda_stack_desc_t;
+
+#define ULLM_CUDA_STACK_FLAG_NO_GRAPH UINT32_C(1) /* launch kernels directly instead of replaying a graph */
+
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_queue_t *queue,
+                                     ullm_cuda_comm_t *comm, const ullm_cuda_stack_desc_t *desc,
+                                     ullm_cuda_stack_t **stack, ullm_cuda_error_sink_t *error_sink);
+/* One pass over all linears for m tokens: input bf16 [m,hidden] -> output bf16
+ * [m, vocab/tp_size] (this rank's slice of the logits).  Enqueue only. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_step(ullm_cuda_stack_t *stack, uint64_t m, ullm_cuda_tensor_t input_bf16,
+                                   ullm_cuda_tensor_t output_bf16, ullm_cuda_error_sink_t *error_sink);
+/* The same pass from and to HOST memory: pinned staging, host->device copy,
+ * the step, device->host copy, and a bounded wait, all inside the call. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_step_host(ullm_cuda_stack_t *stack, uint64_t m, const void *host_input_bf16,
+                                        void *host_output_bf16, uint32_t timeout_ms,
+                                        ullm_cuda_error_sink_t *error_sink);
+
+#define ULLM_CUDA_STACK_LINEAR_QKV UINT32_C(0)
+#define ULLM_CUDA_STACK_LINEAR_O UINT32_C(1)
+#define ULLM_CUDA_STACK_LINEAR_GATE_UP UINT32_C(2)
+#define ULLM_CUDA_STACK_LINEAR_DOWN UINT32_C(3)
+#define ULLM_CUDA_STACK_LINEAR_LM_HEAD UINT32_C(4) /* layer index ignored */
+
+typedef struct ullm_cuda_stack_linear_info_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  ullm_cuda_weight_t weight; /* this rank's shard */
+  uint64_t tensor_id;        /* stream id of the full (unsharded) fp32 weight */
+  uint64_t full_n;
+  uint64_t full_k;
+  uint64_t row_begin; /* shard origin inside the full weight */
+  uint64_t col_begin;
+  ullm_cuda_tensor_t last_input;  /* activation span this linear read in the last step */
+  ullm_cuda_tensor_t last_output; /* and the span it wrote */
+  uint32_t input_dtype;
+  uint32_t output_dtype;
+  uint32_t prologue;
+  uint32_t reserved[5];
+} ullm_cuda_stack_linear_info_t;
+
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_linear_info(ullm_cuda_stack_t *stack, uint32_t layer, uint32_t which,
+                                          ullm_cuda_stack_linear_info_t *info,
+                                          ullm_cuda_error_sink_t *error_sink);
+/* weight + scale bytes this rank streams per step, and kernels per step */
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_stats(ullm_cuda_stack_t *stack, uint64_t *weight_bytes, uint64_t *launches_per_step,
+                                    ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_stack_destroy(ullm_cuda_stack_t **stack, ullm_cuda_error_sink_t *error_sink);
+
+#ifdef __cplusplus
+} /* extern "C" */
+
+#include <cstddef>
+/* layout pins in the style of native/hip/src/evidence_abi.h:66-119 */
+static_assert(sizeof(ullm_cuda_error_sink_t) == 48U, "error sink ABI layout changed");
+static_assert(alignof(ullm_cuda_error_sink_t) == 8U, "error sink ABI alignment changed");
+static_assert(offsetof(ullm_cuda_error_sink_t, message) == 8U, "error sink message offset changed");
+static_assert(offsetof(ullm_cuda_error_sink_t, message_capacity) == 16U, "error sink capacity offset changed");
+static_assert(offsetof(ullm_cuda_error_sink_t, message_length) == 24U, "error sink length offset changed");
+static_assert(offsetof(ullm_cuda_error_sink_t, reserved) == 32U, "error sink reserved offset changed");
+static_assert(sizeof(ullm_cuda_version_info_t) == 32U, "version info ABI layout changed");
+static_assert(sizeof(ullm_cuda_backend_probe_result_t) == 64U, "backend probe ABI layout changed");
+static_assert(sizeof(ullm_cuda_context_probe_result_t) == 32U, "context probe ABI layout changed");
+static_assert(sizeof(ullm_cuda_tensor_t) == 16U, "tensor span ABI layout changed");
+static_assert(sizeof(ullm_cuda_weight_t) == 56U, "weight ABI layout changed");
+static_assert(sizeof(ullm_cuda_completion_result_t) == 56U, "completion result ABI layout changed");
+static_assert(sizeof(ullm_cuda_linear_desc_t) == 160U, "linear descriptor ABI layout changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, weight) == 8U, "linear weight offset changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, m) == 64U, "linear m offset changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, input) == 72U, "linear input offset changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, output) == 96U, "linear output offset changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, input_dtype) == 120U, "linear input_dtype offset changed");
+static_assert(sizeof(ullm_cuda_stack_desc_t) == 88U, "stack descriptor ABI layout changed");
+static_assert(sizeof(ullm_cuda_stack_linear_info_t) == 168U, "stack linear info ABI layout changed");
+#endif
+
+#endif /* ULLM_CUDA_H */

@@ -1,0 +1,269 @@
+// Shared internals of libullm_cuda: boundary helpers (error sink, versioned-struct
+// validation, handle registries) and the runtime objects behind the opaque handles.
+//
+// Boundary rules implemented here follow the reference's host stub:
+//   sink validation without writing a message   native/hip/src/hip_stub.cpp:43-66
+//   write_error truncation / BUFFER_TOO_SMALL   native/hip/src/hip_stub.cpp:17-41
+//   struct_size / abi_version / reserved checks native/hip/src/hip_stub.cpp:69-118
+#pragma once
+
+#include "ullm_cuda.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+namespace ullm {
+
+using sink_t = ullm_cuda_error_sink_t;
+
+// ---- error sink -----------------------------------------------------------
+
+inline ullm_status_t write_error(sink_t *sink, ullm_status_t primary, const char *message) noexcept {
+  if (sink == nullptr) return primary;
+  const size_t len = message == nullptr ? 0U : std::strlen(message);
+  sink->message_length = static_cast<uint64_t>(len);
+  if (sink->message_capacity == 0U) return ULLM_STATUS_BUFFER_TOO_SMALL;
+  if (sink->message == nullptr) return ULLM_STATUS_INVALID_ARGUMENT;
+  const size_t cap = static_cast<size_t>(sink->message_capacity);
+  const size_t n = len < cap - 1U ? len : cap - 1U;
+  if (n != 0U) std::memcpy(sink->message, message, n);
+  sink->message[n] = '\0';
+  return len <= cap - 1U ? primary : ULLM_STATUS_BUFFER_TOO_SMALL;
+}
+
+inline ullm_status_t errorf(sink_t *sink, ullm_status_t primary, const char *fmt, ...) noexcept {
+  char text[512];
+  va_list ap;
+  va_start(ap, fmt);
+  std::vsnprintf(text, sizeof(text), fmt, ap);
+  va_end(ap);
+  return write_error(sink, primary, text);
+}
+
+inline ullm_status_t validate_sink(sink_t *sink) noexcept {
+  if (sink == nullptr) return ULLM_STATUS_OK;
+  if (sink->struct_size < sizeof(sink_t)) return ULLM_STATUS_INVALID_ARGUMENT;
+  if (sink->abi_version != ULLM_CUDA_ABI_VERSION) return ULLM_STATUS_INVALID_ABI_VERSION;
+  if (sink->reserved[0] != 0U || sink->reserved[1] != 0U) return ULLM_STATUS_RESERVED_NONZERO;
+  if (sink->message_capacity > static_cast<uint64_t>(std::numeric_limits<size_t>::max()))
+    return ULLM_STATUS_INVALID_ARGUMENT;
+  if (sink->message_capacity != 0U && sink->message == nullptr) return ULLM_STATUS_INVALID_ARGUMENT;
+  sink->message_length = 0U;
+  if (sink->message != nullptr && sink->message_capacity != 0U) sink->message[0] = '\0';
+  return ULLM_STATUS_OK;
+}
+
+// struct_size / abi_version / reserved, in that order
+template <typename S>
+inline ullm_status_t validate_struct(const S *value, sink_t *sink, const char *what) noexcept {
+  if (value == nullptr) return errorf(sink, ULLM_STATUS_INVALID_ARGUMENT, "%s is null", what);
+  if (value->struct_size < sizeof(S))
+    return errorf(sink, ULLM_STATUS_INVALID_ARGUMENT, "%s: struct_size is smaller than the ABI v1 struct", what);
+  if (value->abi_version != ULLM_CUDA_ABI_VERSION)
+    return errorf(sink, ULLM_STATUS_INVALID_ABI_VERSION, "%s: unsupported ABI version", what);
+  for (size_t i = 0; i < sizeof(value->reserved) / sizeof(value->reserved[0]); ++i)
+    if (value->reserved[i] != 0U)
+      return errorf(sink, ULLM_STATUS_RESERVED_NONZERO, "%s: reserved fields must be zero", what);
+  return ULLM_STATUS_OK;
+}
+
+// ---- runtime objects --------------------------------------------------------
+
+constexpr uint32_t kMagicContext = 0x63747831U, kMagicQueue = 0x71756531U, kMagicBuffer = 0x62756631U,
+                   kMagicCompletion = 0x636d7031U, kMagicGraph = 0x67726131U, kMagicComm = 0x636f6d31U,
+                   kMagicStack = 0x73746b31U;
+
+struct Context {
+  uint32_t magic = kMagicContext;
+  int device = 0;
+  int sm_count = 0;
+  size_t l2_bytes = 0;
+  size_t smem_optin = 0;
+  uint32_t *host_flags = nullptr;    // [16] words, mapped pinned memory
+  uint32_t *device_flags = nullptr;  // device view of host_flags: kernels set a word when a bounded wait expires
+  std::mutex mutex;
+  std::vector<cudaEvent_t> event_pool;
+  std::atomic<uint64_t> live_children{0};
+};
+
+struct Queue {
+  uint32_t magic = kMagicQueue;
+  Context *ctx = nullptr;
+  cudaStream_t stream = nullptr;
+  std::mutex mutex;
+  uint64_t dispatch_count = 0;  // kernels launched since the last signal
+  uint64_t copy_count = 0;
+  uint64_t total_dispatch = 0;
+  bool capturing = false;
+  void *staging = nullptr;  // pinned, kStagingBytes
+};
+constexpr size_t kStagingBytes = size_t(16) << 20;
+
+struct Buffer {
+  uint32_t magic = kMagicBuffer;
+  Context *ctx = nullptr;
+  void *ptr = nullptr;
+  uint64_t size = 0;
+};
+
+struct Completion {
+  uint32_t magic = kMagicCompletion;
+  Queue *queue = nullptr;
+  cudaEvent_t event = nullptr;
+  uint64_t dispatch_count = 0;
+  uint64_t copy_count = 0;
+};
+
+struct Graph {
+  uint32_t magic = kMagicGraph;
+  Context *ctx = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernel_nodes = 0;
+};
+
+// Live-handle registry: a stale, foreign or double-freed handle is answered
+// with ULLM_STATUS_CUDA_INVALID_HANDLE instead of being dereferenced.
+class Registry {
+ public:
+  void add(const void *p) {
+    std::lock_guard<std::mutex> g(m_);
+    live_.insert(p);
+  }
+  bool remove(const void *p) {
+    std::lock_guard<std::mutex> g(m_);
+    return live_.erase(p) != 0;
+  }
+  bool contains(const void *p) {
+    std::lock_guard<std::mutex> g(m_);
+    return p != nullptr && live_.count(p) != 0;
+  }
+
+ private:
+  std::mutex m_;
+  std::unordered_set<const void *> live_;
+};
+Registry &registry();
+
+template <typename T>
+inline T *checked(const void *handle) {
+  return registry().contains(handle) ? const_cast<T *>(static_cast<const T *>(handle)) : nullptr;
+}
+inline Context *as_context(const ullm_cuda_context_t *h) {
+  Context *c = checked<Context>(h);
+  return (c && c->magic == kMagicContext) ? c : nullptr;
+}
+inline Queue *as_queue(const ullm_cuda_queue_t *h) {
+  Queue *q = checked<Queue>(h);
+  return (q && q->magic == kMagicQueue) ? q : nullptr;
+}
+inline Buffer *as_buffer(const ullm_cuda_buffer_t *h) {
+  Buffer *b = checked<Buffer>(h);
+  return (b && b->magic == kMagicBuffer) ? b : nullptr;
+}
+
+// ---- helpers used by every op ------------------------------------------------
+
+ullm_status_t cuda_error(sink_t *sink, cudaError_t e, const char *what) noexcept;
+
+#define ULLM_CUDA_TRY(expr, what)                                     \
+  do {                                                                \
+    cudaError_t ullm_e_ = (expr);                                     \
+    if (ullm_e_ != cudaSuccess) return cuda_error(sink, ullm_e_, what); \
+  } while (0)
+
+// Resolves a span to a device pointer after checking handle, context, alignment and bounds.
+ullm_status_t resolve(const ullm_cuda_tensor_t &t, uint64_t bytes, uint64_t align, const Context *ctx,
+                      const char *what, sink_t *sink, void **out) noexcept;
+
+// Queue acquisition for an op: valid handle, right device made current.
+ullm_status_t begin_op(ullm_cuda_queue_t *queue, sink_t *sink, Queue **out) noexcept;
+// Post-launch check + accounting.
+ullm_status_t end_launch(Queue *q, sink_t *sink, const char *what, uint64_t kernels = 1) noexcept;
+
+// Weight span checks shared by quantise / dequantise / linear.
+struct WeightPtrs {
+  const uint8_t *values = nullptr;
+  const void *scales = nullptr;
+  uint64_t n = 0, k = 0;
+  uint32_t encoding = 0;
+};
+ullm_status_t resolve_weight(const ullm_cuda_weight_t &w, const Context *ctx, sink_t *sink,
+                             WeightPtrs *out) noexcept;
+
+inline uint64_t dtype_bytes(uint32_t dtype) {
+  switch (dtype) {
+    case ULLM_CUDA_DTYPE_BF16:
+    case ULLM_CUDA_DTYPE_F16: return 2;
+    case ULLM_CUDA_DTYPE_F32: return 4;
+    case ULLM_CUDA_DTYPE_F8E4M3FN:
+    case ULLM_CUDA_DTYPE_I8:
+    case ULLM_CUDA_DTYPE_U8: return 1;
+    default: return 0;
+  }
+}
+
+// ---- internal launchers (raw device pointers; arguments already validated) -----
+
+struct LinearArgs {
+  const void *x = nullptr;   // bf16 or f32 [M, x_stride]
+  void *y = nullptr;         // bf16 or f32 [M, y_stride]
+  const uint8_t *w = nullptr;
+  const void *scales = nullptr;
+  uint32_t m = 0;
+  uint32_t n = 0, k = 0;
+  uint64_t x_stride = 0, y_stride = 0;
+  uint32_t encoding = 0;
+  uint32_t x_dtype = 0, y_dtype = 0;
+  uint32_t prologue = 0;
+  float rms_eps = 1e-5f;
+};
+
+// returns the number of kernels launched, or -1 after setting *err
+int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+bool matvec_supports(const LinearArgs &a, const char **why);
+
+int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+bool gemm_supports(const Context *ctx, const LinearArgs &a, const char **why);
+
+int launch_prologue(cudaStream_t stream, const LinearArgs &a, void *x_bf16_out, cudaError_t *err);
+
+void launch_synth_weights(cudaStream_t s, uint64_t seed, uint64_t tensor_id, uint64_t first, uint64_t count,
+                          float std, float *out);
+void launch_synth_activations(cudaStream_t s, uint64_t seed, uint64_t tensor_id, uint64_t first, uint64_t count,
+                              void *out_bf16);
+// Strided variant used by the stack: rows [row0,row0+n) x cols [col0,col0+k) of a [*, full_k] tensor.
+void launch_synth_weight_tile(cudaStream_t s, uint64_t seed, uint64_t tensor_id, uint64_t full_k, uint64_t row0,
+                              uint64_t col0, uint64_t n, uint64_t k, float std, float *out);
+void launch_quantize(cudaStream_t s, const float *src, uint32_t encoding, uint64_t n, uint64_t k, uint8_t *values,
+                     void *scales);
+void launch_aq4_unpack(cudaStream_t s, const uint8_t *values, uint64_t bytes, int8_t *out);
+void launch_aq4_pack(cudaStream_t s, const int8_t *src, uint64_t bytes, uint8_t *values);
+void launch_dequantize(cudaStream_t s, uint32_t encoding, const uint8_t *values, const void *scales, uint64_t n,
+                       uint64_t k, void *out, uint32_t out_dtype);
+
+// comm internals used by the stack
+struct Comm;
+Comm *as_comm(const ullm_cuda_comm_t *h);
+cudaError_t comm_all_reduce_raw(Comm *c, cudaStream_t s, void *data, uint64_t count, uint32_t dtype,
+                                std::string *why);
+uint32_t comm_size(const Comm *c);
+uint32_t comm_rank(const Comm *c);
+
+}  // namespace ullm
+
+#define ULLM_ENTRY_BEGIN try {
+#define ULLM_ENTRY_END(name)                                                                              \
+  }                                                                                                       \
+  catch (...) {                                                                                           \
+    return ullm::write_error(error_sink, ULLM_STATUS_INTERNAL_ERROR, "unexpected exception in " name);    \
+  }

@@ -1,0 +1,162 @@
+// The quantised linear op behind the C ABI: argument validation, kernel selection
+// (decode matvec for M <= 8, tcgen05 GEMM otherwise) and the submit -> wait shape.
+//
+// Reference anchors:
+//   capability query before execution     crates/ullm-core/src/backend.rs:5-24 (Backend::supports)
+//   kernel chosen by op / encoding / shape docs/architecture/runtime.md:83-91
+//   submit returns a completion to wait on native/hip/src/evidence_abi.h:48-59
+//   result report: backend id, dispatch count, fallback_used = 0   native/hip/src/evidence_abi.h:27-40
+// The existing Matmul descriptor rule (same dtype and encoding on every operand,
+// crates/ullm-core/src/op.rs:97-113) rejects a bf16 x quantised-weight product, so
+// this op is an additive "quantised linear" kind with the weight stored [N,K].
+#include "internal.hpp"
+
+namespace ullm {
+
+struct Resolved {
+  LinearArgs args;
+  uint32_t kernel = 0;
+};
+
+static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const Context *ctx, bool need_buffers,
+                                    sink_t *sink, Resolved *out) {
+  ullm_status_t st = validate_struct(desc, sink, "linear descriptor");
+  if (st != ULLM_STATUS_OK) return st;
+  const ullm_cuda_weight_t &w = desc->weight;
+  LinearArgs &a = out->args;
+  if (desc->m == 0) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "M is zero");
+  if (desc->m > (1u << 20)) return write_error(sink, ULLM_STATUS_UNSUPPORTED, "M above 2^20 is not supported");
+  if (desc->input_dtype != ULLM_CUDA_DTYPE_BF16 && desc->input_dtype != ULLM_CUDA_DTYPE_F32)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "input dtype must be BF16 or F32");
+  if (desc->output_dtype != ULLM_CUDA_DTYPE_BF16 && desc->output_dtype != ULLM_CUDA_DTYPE_F32)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "output dtype must be BF16 or F32");
+  if (desc->prologue > ULLM_CUDA_PROLOGUE_SWIGLU)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown prologue");
+  if (desc->kernel > ULLM_CUDA_KERNEL_GEMM) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown kernel id");
+  if (desc->prologue == ULLM_CUDA_PROLOGUE_RMSNORM && !(desc->rms_eps >= 0.0f))
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "rms_eps must be non-negative");
+
+  if (need_buffers) {
+    WeightPtrs wp;
+    st = resolve_weight(w, ctx, sink, &wp);
+    if (st != ULLM_STATUS_OK) return st;
+    a.w = wp.values;
+    a.scales = wp.scales;
+  } else {
+    // shape-only validation: same rules as resolve_weight, without touching handles
+    if (w.encoding == ULLM_CUDA_ENCODING_NVFP4)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 is a descriptor only; no kernel accepts it");
+    if (w.encoding != ULLM_CUDA_ENCODING_AQ4 && w.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight encoding must be AQ4 or FP8_CHANNEL");
+    if (w.n == 0 || w.k == 0) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "weight has a zero extent");
+    if (w.n > 0x7fffffffULL || w.k > 0x7fffffffULL)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight extents above 2^31-1 are not supported");
+    if (w.encoding == ULLM_CUDA_ENCODING_AQ4 && (w.group_size != ULLM_CUDA_AQ4_GROUP || w.k % ULLM_CUDA_AQ4_GROUP))
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "AQ4 needs group size 128 and K a multiple of 128");
+    if (w.encoding == ULLM_CUDA_ENCODING_FP8_CHANNEL && (w.group_size != 0 || w.k % 16))
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "FP8_CHANNEL needs group_size 0 and K a multiple of 16");
+  }
+  a.m = static_cast<uint32_t>(desc->m);
+  a.n = static_cast<uint32_t>(w.n);
+  a.k = static_cast<uint32_t>(w.k);
+  a.encoding = w.encoding;
+  a.x_dtype = desc->input_dtype;
+  a.y_dtype = desc->output_dtype;
+  a.prologue = desc->prologue;
+  a.rms_eps = desc->rms_eps;
+  const uint64_t in_cols = desc->prologue == ULLM_CUDA_PROLOGUE_SWIGLU ? 2 * w.k : w.k;
+  a.x_stride = desc->input_row_stride == 0 ? in_cols : desc->input_row_stride;
+  a.y_stride = desc->output_row_stride == 0 ? w.n : desc->output_row_stride;
+  if (a.x_stride < in_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "input row stride is shorter than a row");
+  if (a.y_stride < w.n) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output row stride is shorter than a row");
+  if (a.x_stride % 8 != 0 || a.y_stride % 2 != 0)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "row strides must keep rows 16-byte (input) / 4-byte (output) aligned");
+
+  if (need_buffers) {
+    const uint64_t xb = dtype_bytes(a.x_dtype), yb = dtype_bytes(a.y_dtype);
+    void *x = nullptr, *y = nullptr;
+    st = resolve(desc->input, ((desc->m - 1) * a.x_stride + in_cols) * xb, 16, ctx, "linear input", sink, &x);
+    if (st != ULLM_STATUS_OK) return st;
+    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + w.n) * yb, 16, ctx, "linear output", sink, &y);
+    if (st != ULLM_STATUS_OK) return st;
+    a.x = x;
+    a.y = y;
+  }
+
+  const char *why_mv = "", *why_gemm = "";
+  const bool mv = matvec_supports(a, &why_mv);
+  const bool gm = gemm_supports(ctx, a, &why_gemm);
+  uint32_t kernel = desc->kernel;
+  if (kernel == ULLM_CUDA_KERNEL_AUTO) kernel = mv ? ULLM_CUDA_KERNEL_MATVEC : (gm ? ULLM_CUDA_KERNEL_GEMM : 0u);
+  if (kernel == ULLM_CUDA_KERNEL_MATVEC && !mv) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "matvec: %s", why_mv);
+  if (kernel == ULLM_CUDA_KERNEL_GEMM && !gm) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "gemm: %s", why_gemm);
+  if (kernel == 0u)
+    return errorf(sink, ULLM_STATUS_UNSUPPORTED, "no kernel serves this shape (matvec: %s; gemm: %s); no CPU fallback",
+                  why_mv, why_gemm);
+  out->kernel = kernel;
+  return ULLM_STATUS_OK;
+}
+
+static ullm_status_t enqueue_resolved(Queue *q, const Resolved &r, sink_t *sink) {
+  cudaError_t e = cudaSuccess;
+  const int launched = r.kernel == ULLM_CUDA_KERNEL_MATVEC ? launch_matvec(q->ctx, q->stream, r.args, &e)
+                                                           : launch_gemm(q->ctx, q->stream, r.args, &e);
+  if (launched < 0) return cuda_error(sink, e, "linear kernel launch");
+  if (launched == 0)
+    return write_error(sink, ULLM_STATUS_CUDA_ZERO_DISPATCH, "linear op launched no kernel");
+  return end_launch(q, sink, "linear kernel launch", static_cast<uint64_t>(launched));
+}
+
+}  // namespace ullm
+
+using namespace ullm;
+
+extern "C" {
+
+ullm_status_t ullm_cuda_linear_supports(const ullm_cuda_linear_desc_t *desc, uint32_t *selected_kernel,
+                                        ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  Resolved r;
+  st = resolve_linear(desc, nullptr, false, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  if (selected_kernel != nullptr) *selected_kernel = r.kernel;
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("linear supports")
+}
+
+ullm_status_t ullm_cuda_linear_enqueue(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                       ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "linear descriptor is null");
+  Queue *q = nullptr;
+  st = begin_op(queue, sink, &q);
+  if (st != ULLM_STATUS_OK) return st;
+  Resolved r;
+  st = resolve_linear(desc, q->ctx, true, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  return enqueue_resolved(q, r, sink);
+  ULLM_ENTRY_END("linear enqueue")
+}
+
+ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                      ullm_cuda_completion_t **completion,
+                                      ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (completion == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "completion output is null");
+  *completion = nullptr;
+  st = ullm_cuda_linear_enqueue(queue, desc, sink);
+  if (st != ULLM_STATUS_OK) return st;
+  return ullm_cuda_queue_signal(queue, completion, sink);
+  ULLM_ENTRY_END("linear submit")
+}
+
+}  // extern "C"

@@ -1,0 +1,608 @@
+// Linear stack of a decoder (per layer: fused QKV, O, gate+up, down; then the LM
+// head), tensor-parallel across ranks, replayed as one CUDA graph per token count.
+//
+// New design: the reference has neither a model graph nor multi-GPU code
+// (docs/plans/main-plan.md:55).  What it fixes is the shape of the boundary: work is
+// enqueued on a queue and observed through a completion (docs/architecture/runtime.md:77-79).
+//
+// Dataflow of one step (no attention is computed; the glue is the minimum that keeps
+// the shapes chained and the magnitudes stable):
+//   h          = input bf16 [m, hidden]
+//   qkv        = QKV( rmsnorm(h) )                      column-parallel, bf16 out
+//   o          = O( qkv[:, :q_local] )                  row-parallel, fp32 out, sum over ranks
+//   gu         = GateUp( rmsnorm(o) )                   column-parallel, bf16 out [gate_l | up_l]
+//   h          = Down( silu(gate_l) * up_l )            row-parallel, fp32 out, sum over ranks
+//   logits     = LMHead( rmsnorm(h) )                   column-parallel, bf16 out [m, vocab/tp]
+// rmsnorm / swiglu run inside the consuming kernel's activation staging.
+//
+// Weights are generated on the device from (seed, tensor id, element index) and
+// quantised there.  FP8 row-parallel shards are cut out of rows quantised over the
+// FULL K, so that every tensor-parallel degree uses the same codes and scales.
+#include "internal.hpp"
+
+#include <chrono>
+#include <map>
+#include <new>
+#include <thread>
+
+namespace ullm {
+
+namespace {
+
+struct StackLinear {
+  uint32_t which = 0, layer = 0;
+  uint64_t tensor_id = 0;
+  uint64_t full_n = 0, full_k = 0;
+  uint64_t n = 0, k = 0;            // shard shape
+  uint64_t row_begin = 0, col_begin = 0;
+  uint64_t values_off = 0, scales_off = 0;  // into the weight buffer
+  bool row_parallel = false;
+  uint32_t prologue = 0, x_dtype = 0, y_dtype = 0;
+  uint64_t in_off = 0, out_off = 0;  // into the activation buffer
+  uint64_t x_stride = 0, y_stride = 0;
+  bool in_is_step_input = false, out_is_step_output = false;
+};
+
+}  // namespace
+
+struct Stack {
+  uint32_t magic = kMagicStack;
+  Context *ctx = nullptr;
+  Queue *queue = nullptr;
+  Comm *comm = nullptr;
+  ullm_cuda_stack_desc_t desc{};
+  std::vector<StackLinear> linears;
+  Buffer *weights = nullptr;   // registered buffers so that linear_info can hand out spans
+  Buffer *acts = nullptr;
+  Buffer *io = nullptr;        // [input | output]
+  uint64_t io_out_off = 0;
+  uint64_t weight_bytes = 0;
+  void *pinned_in = nullptr, *pinned_out = nullptr;
+  cudaEvent_t done = nullptr;
+  std::map<uint32_t, cudaGraphExec_t> graphs;
+  std::map<uint32_t, cudaGraph_t> graph_defs;
+  uint64_t launches_per_step = 0;
+};
+
+namespace {
+
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+uint64_t values_bytes(uint32_t enc, uint64_t n, uint64_t k) { return enc == ULLM_CUDA_ENCODING_AQ4 ? n * (k / 2) : n * k; }
+uint64_t scales_bytes(uint32_t enc, uint64_t n, uint64_t k) {
+  return enc == ULLM_CUDA_ENCODING_AQ4 ? n * (k / 128) * 2 : n * 4;
+}
+
+Buffer *make_buffer(Context *ctx, uint64_t bytes, cudaError_t *err) {
+  Buffer *b = new (std::nothrow) Buffer();
+  if (b == nullptr) {
+    *err = cudaErrorMemoryAllocation;
+    return nullptr;
+  }
+  *err = cudaMalloc(&b->ptr, static_cast<size_t>(bytes));
+  if (*err != cudaSuccess) {
+    delete b;
+    return nullptr;
+  }
+  b->ctx = ctx;
+  b->size = bytes;
+  ctx->live_children++;
+  registry().add(b);
+  return b;
+}
+
+void drop_buffer(Buffer *b) {
+  if (b == nullptr) return;
+  registry().remove(b);
+  (void)cudaFree(b->ptr);
+  b->ctx->live_children--;
+  b->magic = 0;
+  delete b;
+}
+
+// Copies columns [c0, c0+cols) of a row-major [rows, full_cols] byte matrix.
+cudaError_t copy_columns(cudaStream_t s, uint8_t *dst, const uint8_t *src, uint64_t rows, uint64_t full_cols,
+                         uint64_t c0, uint64_t cols) {
+  return cudaMemcpy2DAsync(dst, cols, src + c0, full_cols, cols, rows, cudaMemcpyDeviceToDevice, s);
+}
+
+// Generates and quantises one shard.  Row pieces of the full weight are listed in
+// `pieces` as (first full row, row count); their shard rows are consecutive.
+cudaError_t build_weight(Stack *st, const StackLinear &L, const std::vector<std::pair<uint64_t, uint64_t>> &pieces,
+                         float *scratch_f32, uint8_t *scratch_codes, uint64_t scratch_elems) {
+  cudaStream_t s = st->queue->stream;
+  const uint32_t enc = st->desc.encoding;
+  uint8_t *wbase = static_cast<uint8_t *>(st->weights->ptr);
+  uint8_t *values = wbase + L.values_off;
+  uint8_t *scales = wbase + L.scales_off;
+  const bool full_rows = L.row_parallel && enc == ULLM_CUDA_ENCODING_FP8_CHANNEL && L.k != L.full_k;
+  const uint64_t gen_k = full_rows ? L.full_k : L.k;
+  const uint64_t gen_c0 = full_rows ? 0 : L.col_begin;
+  uint64_t shard_row = 0;
+  for (const auto &pc : pieces) {
+    uint64_t done = 0;
+    while (done < pc.second) {
+      uint64_t rows = scratch_elems / gen_k;
+      if (rows == 0) return cudaErrorInvalidValue;
+      if (rows > pc.second - done) rows = pc.second - done;
+      launch_synth_weight_tile(s, st->desc.seed, L.tensor_id, L.full_k, pc.first + done, gen_c0, rows, gen_k, 0.02f,
+                               scratch_f32);
+      uint8_t *v_dst = values + (enc == ULLM_CUDA_ENCODING_AQ4 ? shard_row * (L.k / 2) : shard_row * L.k);
+      uint8_t *s_dst = scales + (enc == ULLM_CUDA_ENCODING_AQ4 ? shard_row * (L.k / 128) * 2 : shard_row * 4);
+      if (full_rows) {
+        launch_quantize(s, scratch_f32, enc, rows, gen_k, scratch_codes, s_dst);
+        cudaError_t e = copy_columns(s, v_dst, scratch_codes, rows, L.full_k, L.col_begin, L.k);
+        if (e != cudaSuccess) return e;
+      } else {
+        launch_quantize(s, scratch_f32, enc, rows, gen_k, v_dst, s_dst);
+      }
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      done += rows;
+      shard_row += rows;
+    }
+  }
+  return cudaStreamSynchronize(s);
+}
+
+LinearArgs make_args(const Stack *st, const StackLinear &L, uint32_t m) {
+  LinearArgs a;
+  const uint8_t *wbase = static_cast<const uint8_t *>(st->weights->ptr);
+  uint8_t *abase = static_cast<uint8_t *>(st->acts->ptr);
+  uint8_t *iobase = static_cast<uint8_t *>(st->io->ptr);
+  a.w = wbase + L.values_off;
+  a.scales = wbase + L.scales_off;
+  a.x = L.in_is_step_input ? iobase : abase + L.in_off;
+  a.y = L.out_is_step_output ? iobase + st->io_out_off : abase + L.out_off;
+  a.m = m;
+  a.n = static_cast<uint32_t>(L.n);
+  a.k = static_cast<uint32_t>(L.k);
+  a.x_stride = L.x_stride;
+  a.y_stride = L.y_stride;
+  a.encoding = st->desc.encoding;
+  a.x_dtype = L.x_dtype;
+  a.y_dtype = L.y_dtype;
+  a.prologue = L.prologue;
+  a.rms_eps = st->desc.rms_eps;
+  return a;
+}
+
+// Enqueues every kernel of one step on the stack's stream; returns launches or -1.
+int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) {
+  cudaStream_t s = st->queue->stream;
+  int64_t launches = 0;
+  for (const StackLinear &L : st->linears) {
+    const LinearArgs a = make_args(st, L, m);
+    const char *reason = "";
+    int n;
+    if (matvec_supports(a, &reason)) {
+      n = launch_matvec(st->ctx, s, a, err);
+    } else if (gemm_supports(st->ctx, a, &reason)) {
+      n = launch_gemm(st->ctx, s, a, err);
+    } else {
+      *err = cudaErrorNotSupported;
+      if (why) *why = std::string("no kernel serves a stack linear: ") + reason;
+      return -1;
+    }
+    if (n < 0) {
+      if (why) *why = "linear kernel launch failed";
+      return -1;
+    }
+    launches += n;
+    if (L.row_parallel && st->desc.tp_size > 1) {
+      std::string nccl_why;
+      *err = comm_all_reduce_raw(st->comm, s, a.y, static_cast<uint64_t>(m) * L.y_stride, ULLM_CUDA_DTYPE_F32, &nccl_why);
+      if (*err != cudaSuccess) {
+        if (why) *why = "all-reduce failed: " + nccl_why;
+        return -1;
+      }
+      launches += 1;
+    }
+  }
+  *err = cudaSuccess;
+  return launches;
+}
+
+ullm_status_t run_step(Stack *st, uint32_t m, sink_t *sink) {
+  cudaStream_t s = st->queue->stream;
+  cudaError_t e = cudaSuccess;
+  std::string why;
+  if (st->desc.flags & ULLM_CUDA_STACK_FLAG_NO_GRAPH) {
+    const int64_t n = enqueue_step(st, m, &e, &why);
+    if (n < 0) return errorf(sink, e == cudaErrorNotSupported ? ULLM_STATUS_UNSUPPORTED : ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                             "%s (%s)", why.c_str(), cudaGetErrorName(e));
+    st->launches_per_step = static_cast<uint64_t>(n);
+  } else {
+    auto it = st->graphs.find(m);
+    if (it == st->graphs.end()) {
+      ULLM_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+      const int64_t n = enqueue_step(st, m, &e, &why);
+      cudaGraph_t g = nullptr;
+      cudaError_t ce = cudaStreamEndCapture(s, &g);
+      if (n < 0) {
+        if (g) (void)cudaGraphDestroy(g);
+        (void)cudaGetLastError();
+        return errorf(sink, e == cudaErrorNotSupported ? ULLM_STATUS_UNSUPPORTED : ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                      "%s (%s)", why.c_str(), cudaGetErrorName(e));
+      }
+      if (ce != cudaSuccess) return cuda_error(sink, ce, "cudaStreamEndCapture");
+      cudaGraphExec_t ex = nullptr;
+      ce = cudaGraphInstantiate(&ex, g, 0);
+      if (ce != cudaSuccess) {
+        (void)cudaGraphDestroy(g);
+        return cuda_error(sink, ce, "cudaGraphInstantiate");
+      }
+      st->graphs[m] = ex;
+      st->graph_defs[m] = g;
+      st->launches_per_step = static_cast<uint64_t>(n);
+      it = st->graphs.find(m);
+    }
+    ULLM_CUDA_TRY(cudaGraphLaunch(it->second, s), "cudaGraphLaunch");
+  }
+  std::lock_guard<std::mutex> g(st->queue->mutex);
+  st->queue->dispatch_count += st->launches_per_step;
+  st->queue->total_dispatch += st->launches_per_step;
+  return ULLM_STATUS_OK;
+}
+
+Stack *as_stack(const ullm_cuda_stack_t *h) {
+  Stack *s = checked<Stack>(h);
+  return (s && s->magic == kMagicStack) ? s : nullptr;
+}
+
+void destroy_stack(Stack *st) {
+  (void)cudaSetDevice(st->ctx->device);
+  (void)cudaStreamSynchronize(st->queue->stream);
+  for (auto &kv : st->graphs) (void)cudaGraphExecDestroy(kv.second);
+  for (auto &kv : st->graph_defs) (void)cudaGraphDestroy(kv.second);
+  if (st->done) (void)cudaEventDestroy(st->done);
+  if (st->pinned_in) (void)cudaFreeHost(st->pinned_in);
+  if (st->pinned_out) (void)cudaFreeHost(st->pinned_out);
+  drop_buffer(st->weights);
+  drop_buffer(st->acts);
+  drop_buffer(st->io);
+  st->magic = 0;
+  delete st;
+}
+
+}  // namespace
+}  // namespace ullm
+
+using namespace ullm;
+
+extern "C" {
+
+ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_queue_t *queue,
+                                     ullm_cuda_comm_t *comm, const ullm_cuda_stack_desc_t *desc,
+                                     ullm_cuda_stack_t **stack, ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (stack == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "stack output is null");
+  *stack = nullptr;
+  st = validate_struct(desc, sink, "stack descriptor");
+  if (st != ULLM_STATUS_OK) return st;
+  Context *ctx = as_context(context);
+  if (ctx == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "context handle is not live");
+  Queue *q = nullptr;
+  st = begin_op(queue, sink, &q);
+  if (st != ULLM_STATUS_OK) return st;
+  if (q->ctx != ctx) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "queue belongs to another context");
+  const ullm_cuda_stack_desc_t &d = *desc;
+  const uint32_t t = d.tp_size;
+  if (d.encoding != ULLM_CUDA_ENCODING_AQ4 && d.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "stack encoding must be AQ4 or FP8_CHANNEL");
+  if (d.layers == 0 || d.hidden == 0 || d.q_heads == 0 || d.kv_heads == 0 || d.head_dim == 0 || d.ffn == 0 ||
+      d.vocab == 0 || d.max_tokens == 0 || t == 0)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "stack descriptor has a zero extent");
+  if (d.tp_rank >= t) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "tp_rank must be below tp_size");
+  if (d.q_heads % t || d.kv_heads % t || d.ffn % t || d.vocab % t)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "q_heads, kv_heads, ffn and vocab must divide by tp_size");
+  Comm *cm = nullptr;
+  if (t > 1) {
+    cm = as_comm(comm);
+    if (cm == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "tp_size > 1 needs a live comm");
+    if (comm_size(cm) != t || comm_rank(cm) != d.tp_rank)
+      return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "comm rank/size differ from the descriptor");
+  }
+  const uint64_t hd = d.head_dim, qd = uint64_t(d.q_heads) * hd, kvd = uint64_t(d.kv_heads) * hd;
+  const uint64_t ql = qd / t, kvl = kvd / t, fl = uint64_t(d.ffn) / t, vl = uint64_t(d.vocab) / t;
+  const uint64_t kalign = d.encoding == ULLM_CUDA_ENCODING_AQ4 ? 128 : 16;
+  if (d.hidden % kalign || ql % kalign || fl % kalign)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED,
+                       "every per-rank K (hidden, q_heads*head_dim/tp, ffn/tp) must be a multiple of 128 (AQ4) or 16 (FP8)");
+  if ((ql + 2 * kvl) % 8 || (2 * fl) % 8 || vl % 2 || d.hidden % 8)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "per-rank row lengths must keep rows 16-byte aligned");
+
+  Stack *S = new (std::nothrow) Stack();
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_INTERNAL_ERROR, "host allocation failed");
+  S->ctx = ctx;
+  S->queue = q;
+  S->comm = cm;
+  S->desc = d;
+  if (!(S->desc.rms_eps > 0.0f)) S->desc.rms_eps = 1e-5f;
+
+  // ---- plan linears, weight offsets and activation offsets -------------------
+  const uint64_t mt = d.max_tokens;
+  const uint64_t nq = ql + 2 * kvl;
+  uint64_t aoff = 0;
+  auto take_act = [&](uint64_t bytes) {
+    const uint64_t o = aoff;
+    aoff = align_up(aoff + bytes, 256);
+    return o;
+  };
+  const uint64_t act_qkv = take_act(mt * nq * 2);
+  const uint64_t act_o = take_act(mt * d.hidden * 4);
+  const uint64_t act_gu = take_act(mt * 2 * fl * 2);
+  const uint64_t act_h = take_act(mt * d.hidden * 4);
+  uint64_t woff = 0;
+  auto add = [&](uint32_t layer, uint32_t which, uint64_t full_n, uint64_t full_k, uint64_t n, uint64_t k,
+                 uint64_t row_begin, uint64_t col_begin, bool row_parallel) -> StackLinear & {
+    StackLinear L;
+    L.layer = layer;
+    L.which = which;
+    L.tensor_id = (uint64_t(layer) << 8) | which | (1ull << 40);
+    L.full_n = full_n;
+    L.full_k = full_k;
+    L.n = n;
+    L.k = k;
+    L.row_begin = row_begin;
+    L.col_begin = col_begin;
+    L.row_parallel = row_parallel;
+    L.values_off = woff;
+    woff = align_up(woff + values_bytes(d.encoding, n, k), 256);
+    L.scales_off = woff;
+    woff = align_up(woff + scales_bytes(d.encoding, n, k), 256);
+    S->weight_bytes += values_bytes(d.encoding, n, k) + scales_bytes(d.encoding, n, k);
+    S->linears.push_back(L);
+    return S->linears.back();
+  };
+  for (uint32_t l = 0; l < d.layers; ++l) {
+    {
+      StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_QKV, qd + 2 * kvd, d.hidden, nq, d.hidden, d.tp_rank * ql, 0, false);
+      L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
+      L.in_is_step_input = l == 0;
+      L.in_off = act_h;
+      L.x_dtype = l == 0 ? ULLM_CUDA_DTYPE_BF16 : ULLM_CUDA_DTYPE_F32;
+      L.x_stride = d.hidden;
+      L.out_off = act_qkv;
+      L.y_dtype = ULLM_CUDA_DTYPE_BF16;
+      L.y_stride = nq;
+    }
+    {
+      StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_O, d.hidden, qd, d.hidden, ql, 0, d.tp_rank * ql, true);
+      L.prologue = ULLM_CUDA_PROLOGUE_NONE;
+      L.in_off = act_qkv;
+      L.x_dtype = ULLM_CUDA_DTYPE_BF16;
+      L.x_stride = nq;
+      L.out_off = act_o;
+      L.y_dtype = ULLM_CUDA_DTYPE_F32;
+      L.y_stride = d.hidden;
+    }
+    {
+      StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_GATE_UP, 2ull * d.ffn, d.hidden, 2 * fl, d.hidden, d.tp_rank * fl, 0, false);
+      L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
+      L.in_off = act_o;
+      L.x_dtype = ULLM_CUDA_DTYPE_F32;
+      L.x_stride = d.hidden;
+      L.out_off = act_gu;
+      L.y_dtype = ULLM_CUDA_DTYPE_BF16;
+      L.y_stride = 2 * fl;
+    }
+    {
+      StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_DOWN, d.hidden, d.ffn, d.hidden, fl, 0, d.tp_rank * fl, true);
+      L.prologue = ULLM_CUDA_PROLOGUE_SWIGLU;
+      L.in_off = act_gu;
+      L.x_dtype = ULLM_CUDA_DTYPE_BF16;
+      L.x_stride = 2 * fl;
+      L.out_off = act_h;
+      L.y_dtype = ULLM_CUDA_DTYPE_F32;
+      L.y_stride = d.hidden;
+    }
+  }
+  {
+    StackLinear &L = add(0, ULLM_CUDA_STACK_LINEAR_LM_HEAD, d.vocab, d.hidden, vl, d.hidden, d.tp_rank * vl, 0, false);
+    L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
+    L.in_off = act_h;
+    L.x_dtype = ULLM_CUDA_DTYPE_F32;
+    L.x_stride = d.hidden;
+    L.out_is_step_output = true;
+    L.y_dtype = ULLM_CUDA_DTYPE_BF16;
+    L.y_stride = vl;
+  }
+
+  // ---- allocate ----------------------------------------------------------------
+  cudaError_t e = cudaSuccess;
+  S->weights = make_buffer(ctx, woff, &e);
+  if (S->weights) S->acts = make_buffer(ctx, aoff, &e);
+  S->io_out_off = align_up(mt * d.hidden * 2, 256);
+  if (S->acts) S->io = make_buffer(ctx, S->io_out_off + align_up(mt * vl * 2, 256), &e);
+  if (S->io) e = cudaHostAlloc(&S->pinned_in, mt * d.hidden * 2, cudaHostAllocDefault);
+  if (e == cudaSuccess && S->io) e = cudaHostAlloc(&S->pinned_out, mt * vl * 2, cudaHostAllocDefault);
+  if (e == cudaSuccess && S->io) e = cudaEventCreateWithFlags(&S->done, cudaEventDisableTiming);
+  if (e != cudaSuccess || !S->io) {
+    (void)cudaGetLastError();
+    destroy_stack(S);
+    return cuda_error(sink, e, "stack allocation");
+  }
+  (void)cudaMemsetAsync(S->acts->ptr, 0, aoff, q->stream);
+  (void)cudaMemsetAsync(S->io->ptr, 0, S->io->size, q->stream);
+
+  // ---- generate + quantise the weights --------------------------------------------
+  const uint64_t scratch_elems = uint64_t(64) << 20;
+  float *scratch = nullptr;
+  uint8_t *codes = nullptr;
+  e = cudaMalloc(reinterpret_cast<void **>(&scratch), scratch_elems * 4);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&codes), scratch_elems);
+  for (size_t i = 0; e == cudaSuccess && i < S->linears.size(); ++i) {
+    const StackLinear &L = S->linears[i];
+    std::vector<std::pair<uint64_t, uint64_t>> pieces;
+    if (L.which == ULLM_CUDA_STACK_LINEAR_QKV) {
+      pieces.push_back({d.tp_rank * ql, ql});                  // this rank's query heads
+      pieces.push_back({qd + d.tp_rank * kvl, kvl});           // its key heads
+      pieces.push_back({qd + kvd + d.tp_rank * kvl, kvl});     // its value heads
+    } else if (L.which == ULLM_CUDA_STACK_LINEAR_GATE_UP) {
+      pieces.push_back({d.tp_rank * fl, fl});                  // gate rows
+      pieces.push_back({uint64_t(d.ffn) + d.tp_rank * fl, fl});  // up rows
+    } else {
+      pieces.push_back({L.row_begin, L.n});
+    }
+    e = build_weight(S, L, pieces, scratch, codes, scratch_elems);
+  }
+  if (scratch) (void)cudaFree(scratch);
+  if (codes) (void)cudaFree(codes);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    destroy_stack(S);
+    return cuda_error(sink, e, "stack weight generation");
+  }
+  ctx->live_children++;
+  registry().add(S);
+  *stack = reinterpret_cast<ullm_cuda_stack_t *>(S);
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack create")
+}
+
+ullm_status_t ullm_cuda_stack_step(ullm_cuda_stack_t *stack, uint64_t m, ullm_cuda_tensor_t input_bf16,
+                                   ullm_cuda_tensor_t output_bf16, ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  Stack *S = as_stack(stack);
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
+  if (m == 0 || m > S->desc.max_tokens) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "m must be in [1, max_tokens]");
+  ULLM_CUDA_TRY(cudaSetDevice(S->ctx->device), "cudaSetDevice");
+  const uint64_t vl = S->desc.vocab / S->desc.tp_size;
+  const uint64_t in_bytes = m * S->desc.hidden * 2, out_bytes = m * vl * 2;
+  void *in = nullptr, *out = nullptr;
+  st = resolve(input_bf16, in_bytes, 16, S->ctx, "stack input", sink, &in);
+  if (st != ULLM_STATUS_OK) return st;
+  st = resolve(output_bf16, out_bytes, 16, S->ctx, "stack output", sink, &out);
+  if (st != ULLM_STATUS_OK) return st;
+  cudaStream_t s = S->queue->stream;
+  uint8_t *io = static_cast<uint8_t *>(S->io->ptr);
+  ULLM_CUDA_TRY(cudaMemcpyAsync(io, in, in_bytes, cudaMemcpyDeviceToDevice, s), "stack input copy");
+  st = run_step(S, static_cast<uint32_t>(m), sink);
+  if (st != ULLM_STATUS_OK) return st;
+  ULLM_CUDA_TRY(cudaMemcpyAsync(out, io + S->io_out_off, out_bytes, cudaMemcpyDeviceToDevice, s), "stack output copy");
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack step")
+}
+
+ullm_status_t ullm_cuda_stack_step_host(ullm_cuda_stack_t *stack, uint64_t m, const void *host_input_bf16,
+                                        void *host_output_bf16, uint32_t timeout_ms,
+                                        ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  Stack *S = as_stack(stack);
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
+  if (m == 0 || m > S->desc.max_tokens) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "m must be in [1, max_tokens]");
+  if (host_input_bf16 == nullptr || host_output_bf16 == nullptr)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "host pointer is null");
+  ULLM_CUDA_TRY(cudaSetDevice(S->ctx->device), "cudaSetDevice");
+  const uint64_t vl = S->desc.vocab / S->desc.tp_size;
+  const uint64_t in_bytes = m * S->desc.hidden * 2, out_bytes = m * vl * 2;
+  cudaStream_t s = S->queue->stream;
+  uint8_t *io = static_cast<uint8_t *>(S->io->ptr);
+  std::memcpy(S->pinned_in, host_input_bf16, in_bytes);
+  ULLM_CUDA_TRY(cudaMemcpyAsync(io, S->pinned_in, in_bytes, cudaMemcpyHostToDevice, s), "stack input upload");
+  st = run_step(S, static_cast<uint32_t>(m), sink);
+  if (st != ULLM_STATUS_OK) return st;
+  ULLM_CUDA_TRY(cudaMemcpyAsync(S->pinned_out, io + S->io_out_off, out_bytes, cudaMemcpyDeviceToHost, s),
+                "stack output download");
+  ULLM_CUDA_TRY(cudaEventRecord(S->done, s), "cudaEventRecord");
+  {
+    std::lock_guard<std::mutex> g(S->queue->mutex);
+    S->queue->copy_count += 2;
+  }
+  // bounded wait: poll, never block without a deadline
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (uint64_t spins = 0;; ++spins) {
+    cudaError_t e = cudaEventQuery(S->done);
+    if (e == cudaSuccess) break;
+    if (e != cudaErrorNotReady) return cuda_error(sink, e, "cudaEventQuery");
+    if (std::chrono::steady_clock::now() >= deadline)
+      return write_error(sink, ULLM_STATUS_CUDA_TIMEOUT, "stack step not complete before the deadline");
+    if (spins > 20000) std::this_thread::sleep_for(std::chrono::microseconds(20));
+  }
+  std::memcpy(host_output_bf16, S->pinned_out, out_bytes);
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack step host")
+}
+
+ullm_status_t ullm_cuda_stack_linear_info(ullm_cuda_stack_t *stack, uint32_t layer, uint32_t which,
+                                          ullm_cuda_stack_linear_info_t *info,
+                                          ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  st = validate_struct(info, sink, "stack linear info");
+  if (st != ULLM_STATUS_OK) return st;
+  Stack *S = as_stack(stack);
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
+  if (which > ULLM_CUDA_STACK_LINEAR_LM_HEAD) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown linear id");
+  if (which != ULLM_CUDA_STACK_LINEAR_LM_HEAD && layer >= S->desc.layers)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "layer out of range");
+  const size_t idx = which == ULLM_CUDA_STACK_LINEAR_LM_HEAD ? S->linears.size() - 1 : size_t(layer) * 4 + which;
+  const StackLinear &L = S->linears[idx];
+  info->weight.encoding = S->desc.encoding;
+  info->weight.group_size = S->desc.encoding == ULLM_CUDA_ENCODING_AQ4 ? ULLM_CUDA_AQ4_GROUP : 0;
+  info->weight.n = L.n;
+  info->weight.k = L.k;
+  info->weight.values.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(S->weights);
+  info->weight.values.offset_bytes = L.values_off;
+  info->weight.scales.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(S->weights);
+  info->weight.scales.offset_bytes = L.scales_off;
+  info->tensor_id = L.tensor_id;
+  info->full_n = L.full_n;
+  info->full_k = L.full_k;
+  info->row_begin = L.row_begin;
+  info->col_begin = L.col_begin;
+  info->last_input.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(L.in_is_step_input ? S->io : S->acts);
+  info->last_input.offset_bytes = L.in_is_step_input ? 0 : L.in_off;
+  info->last_output.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(L.out_is_step_output ? S->io : S->acts);
+  info->last_output.offset_bytes = L.out_is_step_output ? S->io_out_off : L.out_off;
+  info->input_dtype = L.x_dtype;
+  info->output_dtype = L.y_dtype;
+  info->prologue = L.prologue;
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack linear info")
+}
+
+ullm_status_t ullm_cuda_stack_stats(ullm_cuda_stack_t *stack, uint64_t *weight_bytes, uint64_t *launches_per_step,
+                                    ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  Stack *S = as_stack(stack);
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
+  if (weight_bytes) *weight_bytes = S->weight_bytes;
+  if (launches_per_step) *launches_per_step = S->launches_per_step;
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack stats")
+}
+
+ullm_status_t ullm_cuda_stack_destroy(ullm_cuda_stack_t **stack, ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (stack == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "stack pointer is null");
+  Stack *S = as_stack(*stack);
+  if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
+  registry().remove(S);
+  Context *ctx = S->ctx;
+  destroy_stack(S);
+  ctx->live_children--;
+  *stack = nullptr;
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("stack destroy")
+}
+
+}  // extern "C"
