@@ -163,6 +163,7 @@ def test_graph_capture_replays_a_linear(gpu):
     q.linear_enqueue(d)
     g = q.capture_end()
     q.fill(yb.at(0), 0, m * n * 2)
+    q.synchronize()  # resets the per-signal dispatch counter
     g.launch(q)
     g.launch(q)
     res = q.synchronize()

@@ -12,20 +12,46 @@ pytestmark = pytest.mark.gpu
 TINY = U.StackShape(layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000)
 
 
+def _read(q, span, shape, dtype_id):
+    if dtype_id == U.DTYPE_F32:
+        return q.download(span, shape, np.float32)
+    return o.bf16_bits_to_f32(q.download(span, shape, np.uint16))
+
+
 @pytest.mark.parametrize("encoding,name", [(U.ENCODING_AQ4, "aq4"), (U.ENCODING_FP8_CHANNEL, "fp8")])
 @pytest.mark.parametrize("m", [1, 5, 8])
 @pytest.mark.parametrize("flags", [0, U.STACK_FLAG_NO_GRAPH])
-def test_tiny_stack_matches_numpy_chain(gpu, encoding, name, m, flags):
+def test_tiny_stack_every_linear_matches_the_oracle(gpu, encoding, name, m, flags):
+    """Every one of the 13 linears is checked at the stated tolerance against the oracle
+    applied to the DEVICE's own input of that linear.  (A chain of bf16 roundings is
+    chaotic at the 1-ulp level — one flipped rounding upstream flips a few percent of
+    the roundings downstream — so the end-to-end logits are only held to a loose bound.)"""
     ctx, q = gpu
-    st = U.Stack(ctx, q, TINY, encoding, max_tokens=8, flags=flags)
+    st = U.Stack(ctx, q, TINY, encoding, max_tokens=8, flags=flags | U.STACK_FLAG_KEEP_ACTIVATIONS)
     x = o.synth_activations(SEED, 900 + m, m, TINY.hidden)
     xb = o.f32_to_bf16_bits(x).reshape(m, TINY.hidden)
-    ref = o.stack_reference(SEED, name, TINY.layers, TINY.hidden, TINY.q_heads, TINY.kv_heads, TINY.head_dim,
-                            TINY.ffn, TINY.vocab, x)
+    y = None
     for _ in range(2):  # second pass replays the captured graph
         y = o.bf16_bits_to_f32(st.step_host(xb))
-        stt = o.error_stats(y, ref)
-        assert stt["pass"], stt
+    qd = TINY.q_heads * TINY.head_dim
+    linears = [(l, w) for l in range(TINY.layers) for w in (U.LINEAR_QKV, U.LINEAR_O, U.LINEAR_GATE_UP, U.LINEAR_DOWN)]
+    linears.append((0, U.LINEAR_LM_HEAD))
+    for layer, which in linears:
+        info = st.linear_info(layer, which)
+        n, k = int(info.weight.n), int(info.weight.k)
+        in_cols = {U.LINEAR_O: qd + 2 * TINY.kv_heads * TINY.head_dim, U.LINEAR_DOWN: 2 * k}.get(which, k)
+        xin = _read(q, info.last_input, (m, in_cols), info.input_dtype)
+        if which == U.LINEAR_O:
+            xin = xin[:, :qd]  # the O projection reads the query part of the fused QKV output
+        yout = _read(q, info.last_output, (m, n), info.output_dtype)
+        wdq = o.stack_weight(SEED, layer, which, n, k, name)
+        ref = oracle_linear(xin, wdq, info.prologue, x_is_f32=info.input_dtype == U.DTYPE_F32,
+                            out="f32" if info.output_dtype == U.DTYPE_F32 else "bf16")
+        stt = o.error_stats(yout, ref)
+        assert stt["pass"], (layer, which, stt)
+    ref = o.stack_reference(SEED, name, TINY.layers, TINY.hidden, TINY.q_heads, TINY.kv_heads, TINY.head_dim,
+                            TINY.ffn, TINY.vocab, x)
+    assert np.sqrt(np.mean((y - ref) ** 2)) < 0.02 * np.sqrt(np.mean(ref ** 2))
     # device-resident entry gives the same bits as the host entry
     xin, yout = ctx.alloc(xb.nbytes), ctx.alloc(m * TINY.vocab * 2)
     q.upload(xin.at(0), xb)
@@ -35,7 +61,6 @@ def test_tiny_stack_matches_numpy_chain(gpu, encoding, name, m, flags):
     wb, launches = st.stats()
     assert launches == TINY.layers * 4 + 1
     per = {U.ENCODING_AQ4: lambda n, k: n * k // 2 + n * k // 64, U.ENCODING_FP8_CHANNEL: lambda n, k: n * k + 4 * n}[encoding]
-    qd = TINY.q_heads * TINY.head_dim
     want = TINY.layers * (per(qd + 2 * TINY.kv_heads * TINY.head_dim, TINY.hidden) + per(TINY.hidden, qd)
                           + per(2 * TINY.ffn, TINY.hidden) + per(TINY.hidden, TINY.ffn)) + per(TINY.vocab, TINY.hidden)
     assert wb == want

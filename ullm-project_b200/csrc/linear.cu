@@ -69,15 +69,13 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   a.y_stride = desc->output_row_stride == 0 ? w.n : desc->output_row_stride;
   if (a.x_stride < in_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "input row stride is shorter than a row");
   if (a.y_stride < w.n) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output row stride is shorter than a row");
-  if (a.x_stride % 8 != 0 || a.y_stride % 2 != 0)
-    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "row strides must keep rows 16-byte (input) / 4-byte (output) aligned");
 
   if (need_buffers) {
     const uint64_t xb = dtype_bytes(a.x_dtype), yb = dtype_bytes(a.y_dtype);
     void *x = nullptr, *y = nullptr;
-    st = resolve(desc->input, ((desc->m - 1) * a.x_stride + in_cols) * xb, 16, ctx, "linear input", sink, &x);
+    st = resolve(desc->input, ((desc->m - 1) * a.x_stride + in_cols) * xb, xb, ctx, "linear input", sink, &x);
     if (st != ULLM_STATUS_OK) return st;
-    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + w.n) * yb, 16, ctx, "linear output", sink, &y);
+    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + w.n) * yb, yb, ctx, "linear output", sink, &y);
     if (st != ULLM_STATUS_OK) return st;
     a.x = x;
     a.y = y;

@@ -332,10 +332,16 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     aoff = align_up(aoff + bytes, 256);
     return o;
   };
-  const uint64_t act_qkv = take_act(mt * nq * 2);
-  const uint64_t act_o = take_act(mt * d.hidden * 4);
-  const uint64_t act_gu = take_act(mt * 2 * fl * 2);
-  const uint64_t act_h = take_act(mt * d.hidden * 4);
+  // One set of activation spans shared by all layers, or one set per layer when the
+  // caller wants to read every intermediate back (parity checks).
+  const uint32_t act_sets = (d.flags & ULLM_CUDA_STACK_FLAG_KEEP_ACTIVATIONS) ? d.layers : 1;
+  std::vector<uint64_t> act_qkv_v(act_sets), act_o_v(act_sets), act_gu_v(act_sets), act_h_v(act_sets);
+  for (uint32_t i = 0; i < act_sets; ++i) {
+    act_qkv_v[i] = take_act(mt * nq * 2);
+    act_o_v[i] = take_act(mt * d.hidden * 4);
+    act_gu_v[i] = take_act(mt * 2 * fl * 2);
+    act_h_v[i] = take_act(mt * d.hidden * 4);
+  }
   uint64_t woff = 0;
   auto add = [&](uint32_t layer, uint32_t which, uint64_t full_n, uint64_t full_k, uint64_t n, uint64_t k,
                  uint64_t row_begin, uint64_t col_begin, bool row_parallel) -> StackLinear & {
@@ -359,11 +365,14 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     return S->linears.back();
   };
   for (uint32_t l = 0; l < d.layers; ++l) {
+    const uint32_t si = act_sets == 1 ? 0 : l, sp = act_sets == 1 ? 0 : (l == 0 ? 0 : l - 1);
+    const uint64_t act_qkv = act_qkv_v[si], act_o = act_o_v[si], act_gu = act_gu_v[si], act_h = act_h_v[si];
+    const uint64_t act_h_prev = act_h_v[sp];
     {
       StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_QKV, qd + 2 * kvd, d.hidden, nq, d.hidden, d.tp_rank * ql, 0, false);
       L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
       L.in_is_step_input = l == 0;
-      L.in_off = act_h;
+      L.in_off = act_h_prev;
       L.x_dtype = l == 0 ? ULLM_CUDA_DTYPE_BF16 : ULLM_CUDA_DTYPE_F32;
       L.x_stride = d.hidden;
       L.out_off = act_qkv;
@@ -404,7 +413,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   {
     StackLinear &L = add(0, ULLM_CUDA_STACK_LINEAR_LM_HEAD, d.vocab, d.hidden, vl, d.hidden, d.tp_rank * vl, 0, false);
     L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
-    L.in_off = act_h;
+    L.in_off = act_h_v[act_sets - 1];
     L.x_dtype = ULLM_CUDA_DTYPE_F32;
     L.x_stride = d.hidden;
     L.out_is_step_output = true;

@@ -25,6 +25,7 @@ ENCODING_UNQUANTIZED, ENCODING_NVFP4, ENCODING_AQ4, ENCODING_FP8_CHANNEL = 0, 1,
 PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
 KERNEL_AUTO, KERNEL_MATVEC, KERNEL_GEMM = 0, 1, 2
 STACK_FLAG_NO_GRAPH = 1
+STACK_FLAG_KEEP_ACTIVATIONS = 2
 LINEAR_QKV, LINEAR_O, LINEAR_GATE_UP, LINEAR_DOWN, LINEAR_LM_HEAD = 0, 1, 2, 3, 4
 COMM_ID_BYTES = 128
 
