@@ -260,6 +260,11 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_dequantize(ullm_cuda_queue_t *queue, const
 #define ULLM_CUDA_PROLOGUE_RMSNORM UINT32_C(1) /* x <- bf16(x * rsqrt(mean(x^2) + eps)), weight-free */
 #define ULLM_CUDA_PROLOGUE_SWIGLU UINT32_C(2)  /* input is [M,2K] (gate | up); x <- bf16(silu(gate) * up) */
 
+#define ULLM_CUDA_EPILOGUE_NONE UINT32_C(0)
+/* Weight rows are [gate(N/2) | up(N/2)]; the output is [M, N/2]:
+ * y[m][j] = bf16( silu(g) * u ),  g = bf16(x . W'[j]),  u = bf16(x . W'[N/2 + j]). */
+#define ULLM_CUDA_EPILOGUE_SWIGLU UINT32_C(1)
+
 #define ULLM_CUDA_KERNEL_AUTO UINT32_C(0)
 #define ULLM_CUDA_KERNEL_MATVEC UINT32_C(1) /* CUDA-core streaming kernel, M <= 8 */
 #define ULLM_CUDA_KERNEL_GEMM UINT32_C(2)   /* tcgen05 / TMEM kernel */
@@ -272,13 +277,14 @@ typedef struct ullm_cuda_linear_desc_t {
   ullm_cuda_tensor_t input;
   uint64_t input_row_stride; /* elements; 0 = dense */
   ullm_cuda_tensor_t output;
-  uint64_t output_row_stride; /* elements; 0 = dense (N) */
+  uint64_t output_row_stride; /* elements; 0 = dense (N, or N/2 with the SwiGLU epilogue) */
   uint32_t input_dtype;       /* BF16, or F32 (rounded to bf16 on load) */
   uint32_t output_dtype;      /* BF16 or F32 */
   uint32_t prologue;
   uint32_t kernel;
   float rms_eps;
-  uint32_t reserved[5];
+  uint32_t epilogue;
+  uint32_t reserved[4];
 } ullm_cuda_linear_desc_t;
 
 /* Answers without touching the device: OK, UNSUPPORTED (with a reason in the
@@ -366,7 +372,8 @@ typedef struct ullm_cuda_stack_linear_info_t {
   uint32_t input_dtype;
   uint32_t output_dtype;
   uint32_t prologue;
-  uint32_t reserved[5];
+  uint32_t epilogue;
+  uint32_t reserved[4];
 } ullm_cuda_stack_linear_info_t;
 
 ULLM_CUDA_API ullm_status_t ullm_cuda_stack_linear_info(ullm_cuda_stack_t *stack, uint32_t layer, uint32_t which,

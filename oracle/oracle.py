@@ -364,7 +364,7 @@ def stack_reference(seed, encoding, layers, hidden, q_heads, kv_heads, head_dim,
     """One pass of the linear stack on bf16-valued x [m, hidden] -> logits (bf16
     values) [m, vocab].  Dataflow per layer:
         qkv = QKV(rmsnorm(h));  o = O(qkv[:, :q_dim]) (fp32);
-        gu = GateUp(rmsnorm(bf16(o)));  h = Down(swiglu(gu)) (fp32)
+        act = swiglu(GateUp(rmsnorm(bf16(o))));  h = Down(act) (fp32)
     then logits = LMHead(rmsnorm(bf16(h))).  `trace`, if a dict, receives every
     intermediate under (layer, which)."""
     qd, kvd = q_heads * head_dim, kv_heads * head_dim
@@ -372,8 +372,8 @@ def stack_reference(seed, encoding, layers, hidden, q_heads, kv_heads, head_dim,
     for l in range(layers):
         qkv = linear(rmsnorm(bf16_round(h), eps), stack_weight(seed, l, STACK_QKV, qd + 2 * kvd, hidden, encoding))
         o_ = linear(qkv[:, :qd], stack_weight(seed, l, STACK_O, hidden, qd, encoding), out="f32")
-        gu = linear(rmsnorm(bf16_round(o_), eps), stack_weight(seed, l, STACK_GATE_UP, 2 * ffn, hidden, encoding))
-        h = linear(swiglu(gu), stack_weight(seed, l, STACK_DOWN, hidden, ffn, encoding), out="f32")
+        gu = swiglu(linear(rmsnorm(bf16_round(o_), eps), stack_weight(seed, l, STACK_GATE_UP, 2 * ffn, hidden, encoding)))
+        h = linear(gu, stack_weight(seed, l, STACK_DOWN, hidden, ffn, encoding), out="f32")
         if trace is not None:
             trace[(l, STACK_QKV)], trace[(l, STACK_O)] = qkv, o_
             trace[(l, STACK_GATE_UP)], trace[(l, STACK_DOWN)] = gu, h

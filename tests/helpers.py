@@ -56,12 +56,14 @@ def oracle_dequantize(v, s, encoding):
 
 
 def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_BF16, y_dtype=U.DTYPE_BF16,
-               prologue=U.PROLOGUE_NONE, kernel=U.KERNEL_AUTO, x_stride=0, y_stride=0, submit=True):
+               prologue=U.PROLOGUE_NONE, kernel=U.KERNEL_AUTO, x_stride=0, y_stride=0, submit=True,
+               epilogue=U.EPILOGUE_NONE):
     """x_vals: fp32 array [M, cols] (bf16-representable unless x_dtype is F32).
     Returns (y as fp32 values [M, N], completion result or None)."""
     m, cols = x_vals.shape
     xs = x_stride or cols
-    ys = y_stride or dw.n
+    n_out = dw.n // 2 if epilogue == U.EPILOGUE_SWIGLU else dw.n
+    ys = y_stride or n_out
     xe = 2 if x_dtype == U.DTYPE_BF16 else 4
     ye = 2 if y_dtype == U.DTYPE_BF16 else 4
     xbuf = ctx.alloc(m * xs * xe + 256)
@@ -71,7 +73,8 @@ def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_
     q.upload(xbuf.at(0), o.f32_to_bf16_bits(host).reshape(m, xs) if x_dtype == U.DTYPE_BF16 else host)
     q.fill(ybuf.at(0), CANARY, m * ys * ye + 256)
     d = U.linear_desc(dw.desc, m, xbuf.at(0), ybuf.at(0), input_dtype=x_dtype, output_dtype=y_dtype,
-                      prologue=prologue, kernel=kernel, input_row_stride=x_stride, output_row_stride=y_stride)
+                      prologue=prologue, kernel=kernel, input_row_stride=x_stride, output_row_stride=y_stride,
+                      epilogue=epilogue)
     res = None
     if submit:
         res = q.linear_submit(d).wait(60000)
@@ -85,18 +88,21 @@ def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_
         y = o.bf16_bits_to_f32(body.view(np.uint16)).reshape(m, ys)
     else:
         y = body.view(np.float32).reshape(m, ys)
-    if ys > dw.n:  # padding columns of a strided output must be untouched
-        pad = raw[: m * ys * ye].reshape(m, ys * ye)[:, dw.n * ye:]
+    if ys > n_out:  # padding columns of a strided output must be untouched
+        pad = raw[: m * ys * ye].reshape(m, ys * ye)[:, n_out * ye:]
         assert (pad == CANARY).all(), "kernel wrote into the row padding"
     xbuf.close()
     ybuf.close()
-    return y[:, : dw.n].copy(), res
+    return y[:, :n_out].copy(), res
 
 
-def oracle_linear(x_vals, w_deq, prologue=U.PROLOGUE_NONE, x_is_f32=False, out="bf16", eps=1e-5):
+def oracle_linear(x_vals, w_deq, prologue=U.PROLOGUE_NONE, x_is_f32=False, out="bf16", eps=1e-5,
+                  epilogue=U.EPILOGUE_NONE):
     x = o.bf16_round(x_vals.astype(np.float32)) if x_is_f32 else x_vals
     if prologue == U.PROLOGUE_RMSNORM:
         x = o.rmsnorm(x, eps)
     elif prologue == U.PROLOGUE_SWIGLU:
         x = o.swiglu(x)
+    if epilogue == U.EPILOGUE_SWIGLU:  # rows [gate | up] -> bf16(silu(bf16 gate) * bf16 up)
+        return o.swiglu(o.linear(x, w_deq, out="bf16"))
     return o.linear(x, w_deq, out=out)

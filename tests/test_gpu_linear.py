@@ -78,6 +78,24 @@ def test_prologues_and_dtypes(gpu, encoding, prologue, x_dtype):
 
 
 @pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("m,n,k", [(1, 2, 128), (1, 1030, 1024), (2, 514, 512), (4, 256, 1024), (8, 70, 2048)])
+def test_swiglu_epilogue(gpu, encoding, m, n, k):
+    """Rows [gate(N/2) | up(N/2)] -> [M, N/2] = bf16(silu(bf16 g) * bf16 u)."""
+    ctx, q = gpu
+    w = o.synth_weights(SEED, 740 + n, n, k) * np.float32(3.0)
+    x = o.synth_activations(SEED, 741 + m, m, k)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    v, s = oracle_quantize(w, encoding)
+    ref = oracle_linear(x, oracle_dequantize(v, s, encoding), epilogue=U.EPILOGUE_SWIGLU)
+    y, _ = run_linear(ctx, q, dw, x, epilogue=U.EPILOGUE_SWIGLU, kernel=U.KERNEL_MATVEC)
+    assert y.shape == (m, n // 2)
+    check(y, ref, (encoding, m, n, k))
+    y2, _ = run_linear(ctx, q, dw, x, epilogue=U.EPILOGUE_SWIGLU, y_stride=n // 2 + 6)
+    check(y2, ref)
+    dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
 def test_strided_rows_and_enqueue_path(gpu, encoding):
     ctx, q = gpu
     m, n, k = 4, 96, 512

@@ -39,14 +39,15 @@ def test_tiny_stack_every_linear_matches_the_oracle(gpu, encoding, name, m, flag
     for layer, which in linears:
         info = st.linear_info(layer, which)
         n, k = int(info.weight.n), int(info.weight.k)
-        in_cols = {U.LINEAR_O: qd + 2 * TINY.kv_heads * TINY.head_dim, U.LINEAR_DOWN: 2 * k}.get(which, k)
+        in_cols = {U.LINEAR_O: qd + 2 * TINY.kv_heads * TINY.head_dim}.get(which, k)
         xin = _read(q, info.last_input, (m, in_cols), info.input_dtype)
         if which == U.LINEAR_O:
             xin = xin[:, :qd]  # the O projection reads the query part of the fused QKV output
-        yout = _read(q, info.last_output, (m, n), info.output_dtype)
+        n_out = n // 2 if info.epilogue == U.EPILOGUE_SWIGLU else n
+        yout = _read(q, info.last_output, (m, n_out), info.output_dtype)
         wdq = o.stack_weight(SEED, layer, which, n, k, name)
         ref = oracle_linear(xin, wdq, info.prologue, x_is_f32=info.input_dtype == U.DTYPE_F32,
-                            out="f32" if info.output_dtype == U.DTYPE_F32 else "bf16")
+                            out="f32" if info.output_dtype == U.DTYPE_F32 else "bf16", epilogue=info.epilogue)
         stt = o.error_stats(yout, ref)
         assert stt["pass"], (layer, which, stt)
     ref = o.stack_reference(SEED, name, TINY.layers, TINY.hidden, TINY.q_heads, TINY.kv_heads, TINY.head_dim,
@@ -107,20 +108,22 @@ def test_one_full_width_layer_spot_check(gpu):
         st = U.Stack(ctx, q, shape, encoding, max_tokens=2)
         x = o.synth_activations(SEED, 950, 2, shape.hidden)
         st.step_host(o.f32_to_bf16_bits(x).reshape(2, shape.hidden))
-        for which, k_in_cols, prologue in ((U.LINEAR_DOWN, 2 * 14336, U.PROLOGUE_SWIGLU), (U.LINEAR_GATE_UP, 4096, U.PROLOGUE_RMSNORM)):
+        for which, k_in_cols in ((U.LINEAR_DOWN, 14336), (U.LINEAR_GATE_UP, 4096)):
             info = st.linear_info(0, which)
             n, k = int(info.weight.n), int(info.weight.k)
+            pair = info.epilogue == U.EPILOGUE_SWIGLU
             in_dt = np.float32 if info.input_dtype == U.DTYPE_F32 else np.uint16
             xin = q.download(info.last_input, (2, k_in_cols), in_dt)
             xin = xin if in_dt == np.float32 else o.bf16_bits_to_f32(xin)
             out_dt = np.float32 if info.output_dtype == U.DTYPE_F32 else np.uint16
-            yout = q.download(info.last_output, (2, n), out_dt)
+            yout = q.download(info.last_output, (2, n // 2 if pair else n), out_dt)
             yout = yout if out_dt == np.float32 else o.bf16_bits_to_f32(yout)
-            rows = np.arange(0, n, 331)
+            cols = np.arange(0, n // 2 if pair else n, 331)
+            rows = np.concatenate([cols, n // 2 + cols]) if pair else cols  # gate rows, then the matching up rows
             wr = np.stack([o.synth_weights(SEED, info.tensor_id, 1, k, row0=int(r))[0] for r in rows])
             v, s = oracle_quantize(wr, encoding)
-            ref = oracle_linear(xin, oracle_dequantize(v, s, encoding), prologue, x_is_f32=in_dt == np.float32,
-                                out="f32" if out_dt == np.float32 else "bf16")
-            stt = o.error_stats(yout[:, rows], ref)
+            ref = oracle_linear(xin, oracle_dequantize(v, s, encoding), info.prologue, x_is_f32=in_dt == np.float32,
+                                out="f32" if out_dt == np.float32 else "bf16", epilogue=info.epilogue)
+            stt = o.error_stats(yout[:, cols], ref)
             assert stt["pass"], (encoding, which, stt)
         st.close()

@@ -225,6 +225,7 @@ struct LinearArgs {
   uint32_t encoding = 0;
   uint32_t x_dtype = 0, y_dtype = 0;
   uint32_t prologue = 0;
+  uint32_t epilogue = 0;
   float rms_eps = 1e-5f;
 };
 

@@ -32,6 +32,10 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
     return write_error(sink, ULLM_STATUS_UNSUPPORTED, "output dtype must be BF16 or F32");
   if (desc->prologue > ULLM_CUDA_PROLOGUE_SWIGLU)
     return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown prologue");
+  if (desc->epilogue > ULLM_CUDA_EPILOGUE_SWIGLU)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown epilogue");
+  if (desc->epilogue == ULLM_CUDA_EPILOGUE_SWIGLU && (desc->weight.n % 2 != 0 || desc->output_dtype != ULLM_CUDA_DTYPE_BF16))
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "the SwiGLU epilogue needs an even N and a BF16 output");
   if (desc->kernel > ULLM_CUDA_KERNEL_GEMM) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown kernel id");
   if (desc->prologue == ULLM_CUDA_PROLOGUE_RMSNORM && !(desc->rms_eps >= 0.0f))
     return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "rms_eps must be non-negative");
@@ -64,18 +68,20 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   a.y_dtype = desc->output_dtype;
   a.prologue = desc->prologue;
   a.rms_eps = desc->rms_eps;
+  a.epilogue = desc->epilogue;
+  const uint64_t out_cols = desc->epilogue == ULLM_CUDA_EPILOGUE_SWIGLU ? w.n / 2 : w.n;
   const uint64_t in_cols = desc->prologue == ULLM_CUDA_PROLOGUE_SWIGLU ? 2 * w.k : w.k;
   a.x_stride = desc->input_row_stride == 0 ? in_cols : desc->input_row_stride;
-  a.y_stride = desc->output_row_stride == 0 ? w.n : desc->output_row_stride;
+  a.y_stride = desc->output_row_stride == 0 ? out_cols : desc->output_row_stride;
   if (a.x_stride < in_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "input row stride is shorter than a row");
-  if (a.y_stride < w.n) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output row stride is shorter than a row");
+  if (a.y_stride < out_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output row stride is shorter than a row");
 
   if (need_buffers) {
     const uint64_t xb = dtype_bytes(a.x_dtype), yb = dtype_bytes(a.y_dtype);
     void *x = nullptr, *y = nullptr;
     st = resolve(desc->input, ((desc->m - 1) * a.x_stride + in_cols) * xb, xb, ctx, "linear input", sink, &x);
     if (st != ULLM_STATUS_OK) return st;
-    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + w.n) * yb, yb, ctx, "linear output", sink, &y);
+    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + out_cols) * yb, yb, ctx, "linear output", sink, &y);
     if (st != ULLM_STATUS_OK) return st;
     a.x = x;
     a.y = y;

@@ -10,10 +10,11 @@
 //   h          = input bf16 [m, hidden]
 //   qkv        = QKV( rmsnorm(h) )                      column-parallel, bf16 out
 //   o          = O( qkv[:, :q_local] )                  row-parallel, fp32 out, sum over ranks
-//   gu         = GateUp( rmsnorm(o) )                   column-parallel, bf16 out [gate_l | up_l]
-//   h          = Down( silu(gate_l) * up_l )            row-parallel, fp32 out, sum over ranks
+//   act        = swiglu( GateUp( rmsnorm(o) ) )         column-parallel rows [gate_l | up_l], bf16 out [m, ffn/tp]
+//   h          = Down( act )                            row-parallel, fp32 out, sum over ranks
 //   logits     = LMHead( rmsnorm(h) )                   column-parallel, bf16 out [m, vocab/tp]
-// rmsnorm / swiglu run inside the consuming kernel's activation staging.
+// rmsnorm runs inside the consuming kernel's activation staging, swiglu in the
+// producing kernel's epilogue.
 //
 // Weights are generated on the device from (seed, tensor id, element index) and
 // quantised there.  FP8 row-parallel shards are cut out of rows quantised over the
@@ -37,7 +38,7 @@ struct StackLinear {
   uint64_t row_begin = 0, col_begin = 0;
   uint64_t values_off = 0, scales_off = 0;  // into the weight buffer
   bool row_parallel = false;
-  uint32_t prologue = 0, x_dtype = 0, y_dtype = 0;
+  uint32_t prologue = 0, epilogue = 0, x_dtype = 0, y_dtype = 0;
   uint64_t in_off = 0, out_off = 0;  // into the activation buffer
   uint64_t x_stride = 0, y_stride = 0;
   bool in_is_step_input = false, out_is_step_output = false;
@@ -163,6 +164,7 @@ LinearArgs make_args(const Stack *st, const StackLinear &L, uint32_t m) {
   a.x_dtype = L.x_dtype;
   a.y_dtype = L.y_dtype;
   a.prologue = L.prologue;
+  a.epilogue = L.epilogue;
   a.rms_eps = st->desc.rms_eps;
   return a;
 }
@@ -339,7 +341,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   for (uint32_t i = 0; i < act_sets; ++i) {
     act_qkv_v[i] = take_act(mt * nq * 2);
     act_o_v[i] = take_act(mt * d.hidden * 4);
-    act_gu_v[i] = take_act(mt * 2 * fl * 2);
+    act_gu_v[i] = take_act(mt * fl * 2);
     act_h_v[i] = take_act(mt * d.hidden * 4);
   }
   uint64_t woff = 0;
@@ -392,19 +394,20 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     {
       StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_GATE_UP, 2ull * d.ffn, d.hidden, 2 * fl, d.hidden, d.tp_rank * fl, 0, false);
       L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
+      L.epilogue = ULLM_CUDA_EPILOGUE_SWIGLU;  // writes silu(gate) * up: [m, ffn/tp]
       L.in_off = act_o;
       L.x_dtype = ULLM_CUDA_DTYPE_F32;
       L.x_stride = d.hidden;
       L.out_off = act_gu;
       L.y_dtype = ULLM_CUDA_DTYPE_BF16;
-      L.y_stride = 2 * fl;
+      L.y_stride = fl;
     }
     {
       StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_DOWN, d.hidden, d.ffn, d.hidden, fl, 0, d.tp_rank * fl, true);
-      L.prologue = ULLM_CUDA_PROLOGUE_SWIGLU;
+      L.prologue = ULLM_CUDA_PROLOGUE_NONE;
       L.in_off = act_gu;
       L.x_dtype = ULLM_CUDA_DTYPE_BF16;
-      L.x_stride = 2 * fl;
+      L.x_stride = fl;
       L.out_off = act_h;
       L.y_dtype = ULLM_CUDA_DTYPE_F32;
       L.y_stride = d.hidden;
@@ -579,6 +582,7 @@ ullm_status_t ullm_cuda_stack_linear_info(ullm_cuda_stack_t *stack, uint32_t lay
   info->input_dtype = L.x_dtype;
   info->output_dtype = L.y_dtype;
   info->prologue = L.prologue;
+  info->epilogue = L.epilogue;
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("stack linear info")
 }

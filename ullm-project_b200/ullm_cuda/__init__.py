@@ -19,7 +19,7 @@ from enum import Enum
 import numpy as np
 
 from . import _abi as abi
-from ._abi import (DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_F8E4M3FN, DTYPE_I8, DTYPE_U8, ENCODING_AQ4,  # noqa: F401
+from ._abi import (EPILOGUE_NONE, EPILOGUE_SWIGLU, DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_F8E4M3FN, DTYPE_I8, DTYPE_U8, ENCODING_AQ4,  # noqa: F401
                    ENCODING_FP8_CHANNEL, ENCODING_NVFP4, KERNEL_AUTO, KERNEL_GEMM, KERNEL_MATVEC, LINEAR_DOWN,
                    LINEAR_GATE_UP, LINEAR_LM_HEAD, LINEAR_O, LINEAR_QKV, PROLOGUE_NONE, PROLOGUE_RMSNORM,
                    PROLOGUE_SWIGLU, STACK_FLAG_KEEP_ACTIVATIONS, STACK_FLAG_NO_GRAPH)
@@ -302,7 +302,7 @@ def weight_bytes(encoding: int, n: int, k: int):
 
 def linear_desc(weight: abi.Weight, m: int, x: abi.Tensor, y: abi.Tensor, *, input_dtype=DTYPE_BF16,
                 output_dtype=DTYPE_BF16, prologue=PROLOGUE_NONE, kernel=KERNEL_AUTO, rms_eps=1e-5,
-                input_row_stride=0, output_row_stride=0) -> abi.LinearDesc:
+                input_row_stride=0, output_row_stride=0, epilogue=EPILOGUE_NONE) -> abi.LinearDesc:
     d = abi.LinearDesc()
     d.struct_size = C.sizeof(abi.LinearDesc)
     d.abi_version = abi.ABI_VERSION
@@ -317,6 +317,7 @@ def linear_desc(weight: abi.Weight, m: int, x: abi.Tensor, y: abi.Tensor, *, inp
     d.prologue = prologue
     d.kernel = kernel
     d.rms_eps = rms_eps
+    d.epilogue = epilogue
     return d
 
 

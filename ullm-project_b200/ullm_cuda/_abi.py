@@ -23,6 +23,7 @@ CUDA_DISPATCH_CONTRACT, CUDA_OUT_OF_MEMORY, CUDA_OUT_OF_RANGE, CUDA_COMM_ERROR, 
 DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_F8E4M3FN, DTYPE_I8, DTYPE_U8 = 0, 1, 2, 3, 7, 8
 ENCODING_UNQUANTIZED, ENCODING_NVFP4, ENCODING_AQ4, ENCODING_FP8_CHANNEL = 0, 1, 2, 3
 PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 KERNEL_AUTO, KERNEL_MATVEC, KERNEL_GEMM = 0, 1, 2
 STACK_FLAG_NO_GRAPH = 1
 STACK_FLAG_KEEP_ACTIVATIONS = 2
@@ -72,7 +73,7 @@ class LinearDesc(C.Structure):
     _fields_ = [("struct_size", u32), ("abi_version", u32), ("weight", Weight), ("m", u64), ("input", Tensor),
                 ("input_row_stride", u64), ("output", Tensor), ("output_row_stride", u64), ("input_dtype", u32),
                 ("output_dtype", u32), ("prologue", u32), ("kernel", u32), ("rms_eps", C.c_float),
-                ("reserved", u32 * 5)]
+                ("epilogue", u32), ("reserved", u32 * 4)]
 
 
 class StackDesc(C.Structure):
@@ -86,7 +87,7 @@ class StackLinearInfo(C.Structure):
     _fields_ = [("struct_size", u32), ("abi_version", u32), ("weight", Weight), ("tensor_id", u64), ("full_n", u64),
                 ("full_k", u64), ("row_begin", u64), ("col_begin", u64), ("last_input", Tensor),
                 ("last_output", Tensor), ("input_dtype", u32), ("output_dtype", u32), ("prologue", u32),
-                ("reserved", u32 * 5)]
+                ("epilogue", u32), ("reserved", u32 * 4)]
 
 
 # sizes pinned in the header's static_asserts
