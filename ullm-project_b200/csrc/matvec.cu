@@ -328,7 +328,23 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   pdl_launch_dependents();
 
   uint4 wv[U][R];
+  // AQ4 group scales: lane l keeps the scale of group 32*block + l of each row, one block =
+  // 4096 elements = 4 iterations; a piece fetches its own with one shuffle.
+  constexpr int SB = ENC == AQ4 ? (U + 3) / 4 : 1;
+  __half screg[SB][R];
   auto load_step = [&](uint32_t g, uint32_t it0) {
+    if (ENC == AQ4 && (it0 & 3u) == 0u) {
+#pragma unroll
+      for (int b = 0; b < SB; ++b)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const uint32_t row = row_of(g, r);
+          const uint32_t grp = (it0 / 4 + b) * 32 + lane;
+          screg[b][r] = (row < p.n && grp < p.k / 128)
+                            ? static_cast<const __half *>(p.scales)[(uint64_t)row * (p.k / 128) + grp]
+                            : __float2half(0.0f);
+        }
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t k0 = (it0 + u) * (E * 32) + lane * E;
@@ -422,31 +438,31 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
 #pragma unroll
             for (int m = 0; m < M; ++m) s0[r][m] = s1[r][m] = s2[r][m] = 0;
           const uint32_t pc = it * 32 + lane;
+          // 24 words per activation row: word t = (j*2 + parity)*3 + plane
+          uint32_t xw[M][24];
 #pragma unroll
-          for (int c = 0; c < 6; ++c) {
-            // chunk c holds words t = 4c .. 4c+3, t = (j*2 + parity)*3 + plane
-            uint4 xw[M];
+          for (int m = 0; m < M; ++m)
 #pragma unroll
-            for (int m = 0; m < M; ++m)
-              xw[m] = reinterpret_cast<const uint4 *>(aq.planes + (uint64_t)m * pieces * 24)[(it * 6 + c) * 32 + lane];
+            for (int c = 0; c < 6; ++c) {
+              const uint4 v4 =
+                  reinterpret_cast<const uint4 *>(aq.planes + (uint64_t)m * pieces * 24)[(it * 6 + c) * 32 + lane];
+              xw[m][4 * c] = v4.x, xw[m][4 * c + 1] = v4.y, xw[m][4 * c + 2] = v4.z, xw[m][4 * c + 3] = v4.w;
+            }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int t = 4 * c + q, pl = t % 3, jp = t / 3, j = jp >> 1, par = jp & 1;
+          for (int jp = 0; jp < 8; ++jp) {
+            const int j = jp >> 1, par = jp & 1;
 #pragma unroll
-              for (int r = 0; r < R; ++r) {
-                const uint32_t word = j == 0 ? wv[u][r].x : j == 1 ? wv[u][r].y : j == 2 ? wv[u][r].z : wv[u][r].w;
-                const uint32_t nib = (par == 0 ? word : (word >> 4)) & 0x0f0f0f0fu;
+            for (int r = 0; r < R; ++r) {
+              const uint32_t word = j == 0 ? wv[u][r].x : j == 1 ? wv[u][r].y : j == 2 ? wv[u][r].z : wv[u][r].w;
+              const uint32_t nib = (par == 0 ? word : (word >> 4)) & 0x0f0f0f0fu;
 #pragma unroll
-                for (int m = 0; m < M; ++m) {
-                  const uint32_t xq = q == 0 ? xw[m].x : q == 1 ? xw[m].y : q == 2 ? xw[m].z : xw[m].w;
-                  if (pl == 0) s0[r][m] = dp4a_uu(xq, nib, s0[r][m]);
-                  if (pl == 1) s1[r][m] = dp4a_uu(xq, nib, s1[r][m]);
-                  if (pl == 2) s2[r][m] = dp4a_ss(xq, nib, s2[r][m]);
-                }
+              for (int m = 0; m < M; ++m) {
+                s0[r][m] = dp4a_uu(xw[m][jp * 3], nib, s0[r][m]);
+                s1[r][m] = dp4a_uu(xw[m][jp * 3 + 1], nib, s1[r][m]);
+                s2[r][m] = dp4a_ss(xw[m][jp * 3 + 2], nib, s2[r][m]);
               }
             }
           }
-          const uint32_t k0 = it * (E * 32) + lane * E;
           float pfm[M];
           int xsm[M];
 #pragma unroll
@@ -454,12 +470,11 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
             pfm[m] = aq.pf[m * pieces + pc];
             xsm[m] = aq.xsum[m * pieces + pc];
           }
+          const int sb = U >= 4 ? u / 4 : 0;
+          const int src_lane = (int)((it & 3u) * 8u + (lane >> 2));  // group of this piece within the block
 #pragma unroll
           for (int r = 0; r < R; ++r) {
-            const uint32_t row = row_of(g, r);
-            float sc = 0.0f;
-            if (k0 < p.k && row < p.n)
-              sc = __half2float(static_cast<const __half *>(p.scales)[(uint64_t)row * (p.k / 128) + k0 / 128]);
+            const float sc = __shfl_sync(0xffffffffu, __half2float(screg[sb][r]), src_lane);
 #pragma unroll
             for (int m = 0; m < M; ++m) {
               // sum x*(u-8) as an integer (|.| < 2^30); wrap-around in the partial terms cancels
@@ -598,6 +613,11 @@ cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) 
     const double b1 = pair ? 0.0 : balance(rows, (uint32_t)ctx->sm_count * 32u);
     v = b2 >= b4 ? 8 : 9;
     if (b1 > (b2 > b4 ? b2 : b4) + 0.25) v = 4;  // few, long rows: one row per pass
+    if (ENC == AQ4) {
+      // AQ4 holds more state per row (three integer accumulators): 1024 threads would spill.
+      // Measured best: 4 rows x 2 loads (768 threads) for very tall matrices, else 2 rows x 4 loads.
+      v = rows >= 65536u ? 0 : (p.k >= 8192u ? 11 : 2);
+    }
   }
   if (pair && v >= 4) v = 2;
   switch (v) {
