@@ -1,0 +1,120 @@
+"""GPU parity of the tcgen05 GEMM path (fused AQ4 / FP8 dequantisation) against the oracle,
+at the same tolerance as the matvec: max |y-r| / max(|r|, 0.05 rms(r)) <= 1e-2, mean |y-r| <= 1e-3."""
+import numpy as np
+import pytest
+
+import oracle as o
+import ullm_cuda as U
+from helpers import SEED, DeviceWeight, oracle_dequantize, oracle_linear, oracle_quantize, run_linear
+
+pytestmark = pytest.mark.gpu
+ENCODINGS = [U.ENCODING_AQ4, U.ENCODING_FP8_CHANNEL]
+
+# token counts across every tile width (32/64/128/256) and their edges; N across the 128-row tile edge
+CASES = [(9, 128, 128), (16, 200, 256), (33, 384, 1024), (64, 128, 4096), (100, 130, 512), (128, 256, 2048),
+         (129, 129, 384), (200, 640, 1152), (256, 128, 256), (300, 257, 640), (512, 512, 1024)]
+
+
+def check(y, ref, what=""):
+    st = o.error_stats(y, ref)
+    assert st["pass"], (what, st)
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("m,n,k", CASES)
+def test_gemm_matches_oracle(gpu, encoding, m, n, k):
+    ctx, q = gpu
+    w = o.synth_weights(SEED, 1500 + n + k, n, k)
+    x = o.synth_activations(SEED, 1600 + m + k, m, k)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    v, s = oracle_quantize(w, encoding)
+    wdq = oracle_dequantize(v, s, encoding)
+    y, res = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM)
+    check(y, oracle_linear(x, wdq), (encoding, m, n, k))
+    assert res.dispatch_count >= 1 and res.fallback_used == 0 and res.device_flags == 0
+    yf, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, y_dtype=U.DTYPE_F32)
+    ref64 = oracle_linear(x, wdq, out="f64")
+    assert np.abs(yf - ref64).max() / (np.abs(ref64).max() + 1e-30) < 2e-5
+    assert dw.canaries_intact(q)
+    dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
+def test_gemm_and_matvec_agree(gpu, encoding):
+    """The two kernels implement one op: for M <= 8 both are available and must agree to fp32 noise."""
+    ctx, q = gpu
+    m, n, k = 8, 300, 1024
+    dw = DeviceWeight(ctx, q, o.synth_weights(SEED, 1700, n, k), encoding)
+    x = o.synth_activations(SEED, 1701, m, k)
+    a, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_MATVEC, y_dtype=U.DTYPE_F32)
+    b, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, y_dtype=U.DTYPE_F32)
+    assert np.abs(a - b).max() / np.abs(a).max() < 1e-5
+    dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("prologue,x_dtype", [(U.PROLOGUE_RMSNORM, U.DTYPE_F32), (U.PROLOGUE_RMSNORM, U.DTYPE_BF16),
+                                               (U.PROLOGUE_SWIGLU, U.DTYPE_BF16), (U.PROLOGUE_NONE, U.DTYPE_F32)])
+def test_gemm_prologues(gpu, encoding, prologue, x_dtype):
+    ctx, q = gpu
+    m, n, k = 40, 256, 512
+    cols = 2 * k if prologue == U.PROLOGUE_SWIGLU else k
+    w = o.synth_weights(SEED, 1710, n, k)
+    xs = o.synth_normal(SEED, 1711, 0, m * cols).reshape(m, cols) * np.float32(1.3)
+    x = xs if x_dtype == U.DTYPE_F32 else o.bf16_round(xs)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    v, s = oracle_quantize(w, encoding)
+    ref = oracle_linear(x, oracle_dequantize(v, s, encoding), prologue, x_is_f32=x_dtype == U.DTYPE_F32)
+    y, _ = run_linear(ctx, q, dw, x, x_dtype=x_dtype, prologue=prologue, kernel=U.KERNEL_GEMM)
+    check(y, ref, (encoding, prologue, x_dtype))
+    dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
+def test_gemm_swiglu_epilogue_and_strides(gpu, encoding):
+    ctx, q = gpu
+    m, n, k = 70, 512, 256
+    w = o.synth_weights(SEED, 1720, n, k) * np.float32(3.0)
+    x = o.synth_activations(SEED, 1721, m, k)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    v, s = oracle_quantize(w, encoding)
+    wdq = oracle_dequantize(v, s, encoding)
+    y, _ = run_linear(ctx, q, dw, x, epilogue=U.EPILOGUE_SWIGLU, kernel=U.KERNEL_GEMM, y_stride=n // 2 + 8)
+    check(y, oracle_linear(x, wdq, epilogue=U.EPILOGUE_SWIGLU))
+    y2, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, x_stride=k + 24, y_stride=n + 10)
+    check(y2, oracle_linear(x, wdq))
+    dw.close()
+
+
+def test_auto_selects_gemm_above_eight_tokens(gpu):
+    ctx, q = gpu
+    w = U.abi.Weight(U.ENCODING_FP8_CHANNEL, 0, 256, 512, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))
+    assert U.linear_supports(U.linear_desc(w, 8, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))) == U.KERNEL_MATVEC
+    assert U.linear_supports(U.linear_desc(w, 9, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))) == U.KERNEL_GEMM
+
+
+def test_prefill_shape_on_sampled_rows(gpu):
+    """M = 2048 tokens against K = 4096, N = 14336 (and the transposed down projection), generated and
+    quantised on the device; a strided sample of output channels is recomputed by the oracle."""
+    ctx, q = gpu
+    m = 2048
+    x = o.synth_activations(SEED, 1730, m, 14336)
+    for encoding in ENCODINGS:
+        for n, k in ((14336, 4096), (4096, 14336)):
+            src = ctx.alloc(n * k * 4)
+            q.synth_weights(SEED, 1740 + encoding, 0, n * k, 0.02, src.at(0))
+            vb, sb = U.weight_bytes(encoding, n, k)
+            vals, scl = ctx.alloc(vb), ctx.alloc(sb)
+            wd = U.weight_desc(encoding, n, k, vals.at(0), scl.at(0))
+            q.quantize(src.at(0), wd)
+            xb, yb = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+            q.upload(xb.at(0), o.f32_to_bf16_bits(x[:, :k]))
+            res = q.linear_submit(U.linear_desc(wd, m, xb.at(0), yb.at(0))).wait(120000)
+            assert res.device_flags == 0
+            y = o.bf16_bits_to_f32(q.download(yb.at(0), (m, n), np.uint16))
+            rows = np.arange(5, n, 997)
+            wr = np.stack([o.synth_weights(SEED, 1740 + encoding, 1, k, row0=int(r))[0] for r in rows])
+            v, s = oracle_quantize(wr, encoding)
+            check(y[:, rows], o.linear(np.ascontiguousarray(x[:, :k]), oracle_dequantize(v, s, encoding)), (encoding, n, k))
+            for b in (src, vals, scl, xb, yb):
+                b.close()

@@ -90,6 +90,8 @@ struct Context {
   size_t smem_optin = 0;
   uint32_t *host_flags = nullptr;    // [16] words, mapped pinned memory
   uint32_t *device_flags = nullptr;  // device view of host_flags: kernels set a word when a bounded wait expires
+  void *scratch = nullptr;           // grow-only device scratch of the GEMM path (prologue output, gate|up)
+  size_t scratch_bytes = 0;
   std::mutex mutex;
   std::vector<cudaEvent_t> event_pool;
   std::atomic<uint64_t> live_children{0};
@@ -234,6 +236,10 @@ int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, 
 bool matvec_supports(const LinearArgs &a, const char **why);
 
 int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+// Scratch bytes launch_gemm needs for these arguments, and a way to reserve them ahead of
+// time (the scratch may not grow while a stream is being captured).
+size_t gemm_scratch_bytes(const LinearArgs &a);
+cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes);
 bool gemm_supports(const Context *ctx, const LinearArgs &a, const char **why);
 
 int launch_prologue(cudaStream_t stream, const LinearArgs &a, void *x_bf16_out, cudaError_t *err);

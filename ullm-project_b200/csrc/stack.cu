@@ -441,6 +441,21 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   (void)cudaMemsetAsync(S->acts->ptr, 0, aoff, q->stream);
   (void)cudaMemsetAsync(S->io->ptr, 0, S->io->size, q->stream);
 
+  // ---- reserve the GEMM path's scratch for the largest step (it cannot grow during capture) ----
+  if (d.max_tokens > 8) {
+    size_t need = 0;
+    for (const StackLinear &L : S->linears) {
+      const size_t b = gemm_scratch_bytes(make_args(S, L, d.max_tokens));
+      need = b > need ? b : need;
+    }
+    e = gemm_reserve_scratch(ctx, need);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      destroy_stack(S);
+      return cuda_error(sink, e, "stack scratch allocation");
+    }
+  }
+
   // ---- generate + quantise the weights --------------------------------------------
   const uint64_t scratch_elems = uint64_t(64) << 20;
   float *scratch = nullptr;
