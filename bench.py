@@ -207,6 +207,66 @@ def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps):
     return {"us_per_launch": us, "algorithmic_bytes": algo, "gbs": algo / us / 1e3, "weight_copies": copies}
 
 
+def tensor_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured (MEASURED_PEAKS.json)"
+    return 1590.0, 1400.0, "fallback (1.59 PFLOP/s burst, earlier measurement on this pool)"
+
+
+def time_gemm(U, ctx, q, enc_id, m, n, k, reps):
+    """Device time of one fused-dequant GEMM launch (tcgen05 path), activations [m,k] bf16 resident in HBM."""
+    vb, sb = U.weight_bytes(enc_id, n, k)
+    src = ctx.alloc(n * k * 4)
+    q.synth_weights(SEED, 4300, 0, n * k, 0.02, src.at(0))
+    v, s = ctx.alloc(vb), ctx.alloc(sb)
+    wd = U.weight_desc(enc_id, n, k, v.at(0), s.at(0))
+    q.quantize(src.at(0), wd)
+    src.close()
+    xb, yb = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+    q.synth_activations(SEED, 4301, 0, m * k, xb.at(0))
+    d = U.linear_desc(wd, m, xb.at(0), yb.at(0), kernel=U.KERNEL_GEMM)
+    for _ in range(3):
+        q.linear_enqueue(d)
+    q.synchronize()
+    a = q.signal()
+    for _ in range(reps):
+        q.linear_enqueue(d)
+    b = q.signal()
+    b.query(600000)
+    ms = b.elapsed_ms_since(a) / reps
+    a.close()
+    b.close()
+    for buf in (v, s, xb, yb):
+        buf.close()
+    flops = 2.0 * m * n * k
+    return {"us_per_launch": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12, "flops": flops,
+            "weight_gbs": (vb + sb) / (ms * 1e-3) / 1e9}
+
+
+def run_single_gemm(U, args):
+    """One GEMM shape on one GPU: M = --batch tokens, weight [--n, --k]; prints TFLOP/s against the
+    measured cuBLAS bf16 peak (burst: the kernel is timed alone)."""
+    ctx = U.Context(0)
+    q = ctx.queue()
+    enc_id = U.ENCODING_AQ4 if args.enc == "aq4" else U.ENCODING_FP8_CHANNEL
+    r = time_gemm(U, ctx, q, enc_id, args.batch, args.n, args.k, reps=max(args.steps, 1))
+    burst, sustained, src = tensor_peaks()
+    print(json.dumps({
+        "metric": "fused-dequant GEMM TFLOP/s", "value": r["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": 3, "ms_per_step": r["us_per_launch"] / 1e3, "higher_is_better": True,
+        "config": {"workload": f"{args.enc} GEMM M={args.batch} N={args.n} K={args.k}"},
+        "roofline": {"bound": "tensor", "achieved": r["tflops"], "peak": burst, "unit": "TFLOP/s",
+                     "frac": r["tflops"] / burst, "traffic": None, "peak_source": src,
+                     "frac_of_sustained": r["tflops"] / sustained, "frac_of_nominal_2250": r["tflops"] / 2250.0,
+                     "weight_stream_gbs": r["weight_gbs"]},
+        "gpu_launches": max(args.steps, 1) + 3}), flush=True)
+    q.close()
+    ctx.close()
+
+
 def run_single_matvec(U, args):
     """One matvec shape on one GPU (the case the ncu captures use): `--steps` graph replays over
     weight copies that together exceed 2x L2; prints achieved HBM GB/s against the measured peak."""
@@ -233,7 +293,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS) + ["matvec"])
+    ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS) + ["matvec", "gemm"])
     ap.add_argument("--enc", default="fp8", choices=["fp8", "aq4"], help="matvec workload: weight encoding")
     ap.add_argument("--n", type=int, default=57344, help="matvec workload: output channels")
     ap.add_argument("--k", type=int, default=8192, help="matvec workload: reduction length")
@@ -247,6 +307,9 @@ def main():
 
     if args.workload == "matvec":
         run_single_matvec(U, args)
+        return
+    if args.workload == "gemm":
+        run_single_gemm(U, args)
         return
     shape_name, enc, descr = WORKLOADS[args.workload]
     shape = getattr(U, shape_name)

@@ -15,10 +15,10 @@
 // One CTA per SM computes one 128 x TT tile; warp roles:
 //   warp 0      TMA: activation tiles [TT x 64] bf16, 128-byte swizzle, completion on an mbarrier
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (kind::f16, bf16 x bf16 -> f32)
-//   warps 2-5   weight producers: thread r streams row n0 + r from global memory (16-byte loads,
-//               two k-tiles ahead), converts to EXACT bf16 (e4m3 -> bf16; 4-bit q -> bf16 integer)
-//               and writes the K-major, 128-byte-swizzled A tile the MMA reads
-//   warps 6-13  epilogue: tcgen05.ld, scale, convert, store
+//   warps 2-9   weight producers: two threads per row n0 + r stream it from global memory (16-byte
+//               loads, two k-tiles ahead), convert to EXACT bf16 (e4m3 -> bf16; 4-bit q -> bf16
+//               integer) and write the K-major, 128-byte-swizzled A tile the MMA reads
+//   warps 10-17 epilogue: tcgen05.ld, scale, convert, store
 // FP8: all of K accumulates in one tensor-memory buffer; scale[n] is applied once at the end.
 // AQ4: products of bf16 activations with integers -7..7 are exact, so a 128-deep group is
 // accumulated unscaled, drained, and added into fp32 registers as scale[n,g] * partial; two
@@ -40,8 +40,9 @@ constexpr uint32_t AQ4 = ULLM_CUDA_ENCODING_AQ4;
 constexpr uint32_t FP8 = ULLM_CUDA_ENCODING_FP8_CHANNEL;
 constexpr int BM = 128;  // weight rows per tile (MMA M)
 constexpr int BK = 64;   // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 14 * 32;
-constexpr int kProducerWarp0 = 2, kEpilogueWarp0 = 6;
+constexpr int kProducerWarps = 8;
+constexpr int kProducerWarp0 = 2, kEpilogueWarp0 = kProducerWarp0 + kProducerWarps;
+constexpr int kThreads = (kEpilogueWarp0 + 8) * 32;
 constexpr uint32_t kFlagGemmWait = 2u;
 constexpr uint64_t kWaitLimitNs = 20ull * 1000ull * 1000ull * 1000ull;
 
@@ -178,12 +179,19 @@ __device__ __forceinline__ void fp8x4_to_bf16x4(uint32_t w, uint32_t &lo, uint32
 // eight nibbles (one word, element 2i in the low nibble of byte i) -> four words of two bf16 integers q = u - 8
 __device__ __forceinline__ void aq4x8_to_bf16x8(uint32_t w, uint32_t (&out)[4]) {
   const __nv_bfloat162 bias = __floats2bfloat162_rn(136.0f, 136.0f);
+  const uint32_t lo = w & 0x0f0f0f0fu;         // u of elements 0,2,4,6, one per byte
+  const uint32_t hi = (w >> 4) & 0x0f0f0f0fu;  // u of elements 1,3,5,7
+  const uint32_t t03 = __byte_perm(lo, hi, 0x5140);  // bytes u0,u1,u2,u3
+  const uint32_t t47 = __byte_perm(lo, hi, 0x7362);  // bytes u4,u5,u6,u7
+  // 0x4300 | u is the bf16 number 128 + u (exact for u < 128): widen each byte with a 0x43 high byte
+  uint32_t v[4];
+  v[0] = __byte_perm(t03, 0x43434343u, 0x4140);
+  v[1] = __byte_perm(t03, 0x43434343u, 0x4342);
+  v[2] = __byte_perm(t47, 0x43434343u, 0x4140);
+  v[3] = __byte_perm(t47, 0x43434343u, 0x4342);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint32_t b = w >> (8 * i);
-    // 0x4300 | u is the bf16 number 128 + u (exact for u < 128)
-    const uint32_t u = 0x43004300u | (b & 0xfu) | ((b << 12) & 0xf0000u);
-    const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&u), bias);
+    const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v[i]), bias);
     out[i] = *reinterpret_cast<const uint32_t *>(&q);
   }
 }
@@ -194,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   constexpr uint32_t A_BYTES = BM * BK * 2;           // 16 KiB
   constexpr uint32_t B_BYTES = (uint32_t)TT * BK * 2;  // TT x 128 B
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t RAW16 = ENC == AQ4 ? 2 : 4;  // 16-byte loads of one row per k-tile
+  constexpr uint32_t RAW16 = ENC == AQ4 ? 1 : 2;  // 16-byte loads of half a row per k-tile
   constexpr int ACC_BUFS = ENC == AQ4 ? 2 : 1;
   constexpr uint32_t TMEM_COLS = (uint32_t)(TT * ACC_BUFS) < 32u ? 32u : (uint32_t)(TT * ACC_BUFS);
   constexpr int MAX_STAGES = 8;
@@ -218,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (threadIdx.x == 0) {
     abort_flag = 0u;
     for (uint32_t s = 0; s < NS; ++s) {
-      mbar_init(full_a(s), 4u);  // one arrival per producer warp
+      mbar_init(full_a(s), (uint32_t)kProducerWarps);  // one arrival per producer warp
       mbar_init(full_b(s), 1u);  // the TMA thread's expect_tx
       mbar_init(empty(s), 1u);   // tcgen05.commit
     }
@@ -290,18 +298,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       }
     }
   } else if (warp < kEpilogueWarp0) {
-    // ---- weight producers: thread r owns row n0 + r of the tile ---------------------------
-    const uint32_t r = threadIdx.x - kProducerWarp0 * 32;
+    // ---- weight producers: threads 2r and 2r+1 own the two halves of row n0 + r of the tile -----
+    const uint32_t pt = threadIdx.x - kProducerWarp0 * 32;
+    const uint32_t r = pt >> 1, hf = pt & 1u;
     const uint32_t row = n0 + r;
     const bool valid = row < p.n;
     const uint32_t row_bytes = ENC == AQ4 ? p.k / 2 : p.k;
-    const uint8_t *src = p.w + (uint64_t)(valid ? row : 0) * row_bytes;
+    const uint8_t *src = p.w + (uint64_t)(valid ? row : 0) * row_bytes + hf * (RAW16 * 16);
     constexpr int PF = 2;  // k-tiles of raw bytes kept in registers ahead of the one being converted
     uint4 raw[PF][RAW16];
     auto fetch = [&](uint32_t kt, int j) {
 #pragma unroll
       for (uint32_t i = 0; i < RAW16; ++i)
-        raw[j][i] = (valid && kt < ktiles) ? ldg_stream(src + (uint64_t)kt * (RAW16 * 16) + i * 16) : make_uint4(0, 0, 0, 0);
+        raw[j][i] = (valid && kt < ktiles) ? ldg_stream(src + (uint64_t)kt * (2 * RAW16 * 16) + i * 16) : make_uint4(0, 0, 0, 0);
     };
 #pragma unroll
     for (int j = 0; j < PF; ++j) fetch((uint32_t)j, j);
@@ -312,29 +321,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (kt + j >= ktiles) break;
         if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) goto done;
         const uint32_t a_row = smem0 + slot * STAGE_BYTES + r * 128u;
-        if (ENC == FP8) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {  // chunk c = k 8c..8c+7 = raw bytes 8c..8c+7
-            const uint4 q = raw[j][c >> 1];
-            const uint32_t w0 = (c & 1) ? q.z : q.x, w1 = (c & 1) ? q.w : q.y;
-            uint32_t o0, o1, o2, o3;
-            fp8x4_to_bf16x4(w0, o0, o1);
-            fp8x4_to_bf16x4(w1, o2, o3);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((uint32_t)c ^ (r & 7u)) << 4)), "r"(o0),
-                         "r"(o1), "r"(o2), "r"(o3)
-                         : "memory");
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {  // chunk c = k 8c..8c+7 = one word of nibbles
-            const uint4 q = raw[j][c >> 2];
-            const uint32_t w = (c & 3) == 0 ? q.x : (c & 3) == 1 ? q.y : (c & 3) == 2 ? q.z : q.w;
-            uint32_t o[4];
+        for (int i = 0; i < 4; ++i) {  // chunk c = k 8c..8c+7 of this k-tile; this thread owns c = 4*hf + i
+          const uint32_t c = 4u * hf + (uint32_t)i;
+          uint32_t o[4];
+          if (ENC == FP8) {  // 8 raw bytes = 2 words
+            const uint4 q = raw[j][i >> 1];
+            const uint32_t w0 = (i & 1) ? q.z : q.x, w1 = (i & 1) ? q.w : q.y;
+            fp8x4_to_bf16x4(w0, o[0], o[1]);
+            fp8x4_to_bf16x4(w1, o[2], o[3]);
+          } else {  // 8 nibbles = 1 word
+            const uint4 q = raw[j][0];
+            const uint32_t w = i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
             aq4x8_to_bf16x8(w, o);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((uint32_t)c ^ (r & 7u)) << 4)), "r"(o[0]),
-                         "r"(o[1]), "r"(o[2]), "r"(o[3])
-                         : "memory");
           }
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + ((c ^ (r & 7u)) << 4)), "r"(o[0]),
+                       "r"(o[1]), "r"(o[2]), "r"(o[3])
+                       : "memory");
         }
         fetch(kt + j + PF, j);  // refill the register slot just consumed
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
