@@ -16,7 +16,7 @@
 //   warp 0      TMA: activation tiles [TT x 64] bf16, 128-byte swizzle, completion on an mbarrier
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (kind::f16, bf16 x bf16 -> f32)
 //   warps 2-9   weight producers: two threads per row n0 + r stream it from global memory (16-byte
-//               loads, two k-tiles ahead), convert to EXACT bf16 (e4m3 -> bf16; 4-bit q -> bf16
+//               loads, four to eight k-tiles ahead), convert to EXACT bf16 (e4m3 -> bf16; 4-bit q -> bf16
 //               integer) and write the K-major, 128-byte-swizzled A tile the MMA reads
 //   warps 10-17 epilogue: tcgen05.ld, scale, convert, store
 // FP8: all of K accumulates in one tensor-memory buffer; scale[n] is applied once at the end.
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const bool valid = row < p.n;
     const uint32_t row_bytes = ENC == AQ4 ? p.k / 2 : p.k;
     const uint8_t *src = p.w + (uint64_t)(valid ? row : 0) * row_bytes + hf * (RAW16 * 16);
-    constexpr int PF = 2;  // k-tiles of raw bytes kept in registers ahead of the one being converted
+    constexpr int PF = ENC == AQ4 ? 8 : 4;  // k-tiles of raw bytes kept in registers ahead of the one being converted
     uint4 raw[PF][RAW16];
     auto fetch = [&](uint32_t kt, int j) {
 #pragma unroll

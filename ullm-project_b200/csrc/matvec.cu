@@ -619,7 +619,7 @@ cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) 
       v = rows >= 65536u ? 0 : (p.k >= 8192u ? 11 : 2);
     }
   }
-  if (pair && v >= 4) v = 2;
+  if (pair && (v == 4 || v == 5)) v = 2;  // the SwiGLU epilogue needs an even number of rows per pass
   switch (v) {
     case 0: return launch_one<1, 4, 2, ENC, 768>(ctx, stream, p);
     case 1: return launch_one<1, 4, 1, ENC, 1024>(ctx, stream, p);
