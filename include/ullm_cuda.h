@@ -299,6 +299,26 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, co
                                       ullm_cuda_completion_t **completion,
                                       ullm_cuda_error_sink_t *error_sink);
 
+/* No counterpart in the reference.  The same op as ullm_cuda_linear_enqueue on the tensor-core
+ * (GEMM) kernel, for callers that must not trigger a device allocation: a serving loop that has
+ * handed all free HBM to its own pool (so cudaMalloc would fail or fragment it), or a thread that
+ * cannot afford the implicit device-wide synchronisation an allocation or a free may cause.
+ * The GEMM path stages prologue(x) as bf16 before the tensor cores read it; here that staging
+ * area is a fixed ULLM_CUDA_STATIC_SCRATCH_BYTES array compiled into the library (every GPU that
+ * loads the library carries it until the process exits) instead of the context's growable scratch.
+ *   - M * K * 2 bytes must fit ULLM_CUDA_STATIC_SCRATCH_BYTES, else ULLM_STATUS_UNSUPPORTED;
+ *     the SwiGLU epilogue is not offered here (ULLM_STATUS_UNSUPPORTED).
+ *   - The first call on each device looks the array's device address up once; make that first
+ *     call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the previous call left:
+ *     nothing in it needs zeroing (each call overwrites exactly what it reads back), but two calls
+ *     whose kernels can overlap on the GPU (different queues) race on it — serialise them.
+ *   - No cudaMalloc / cudaFree / allocating library routine is called. */
+#define ULLM_CUDA_STATIC_SCRATCH_BYTES (UINT64_C(8) << 20)
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_queue_t *queue,
+                                                                    const ullm_cuda_linear_desc_t *desc,
+                                                                    ullm_cuda_error_sink_t *error_sink);
+
 /* ---- tensor-parallel communicator (NCCL, loaded at run time) ------------------- */
 #define ULLM_CUDA_COMM_ID_BYTES 128
 ULLM_CUDA_API ullm_status_t ullm_cuda_comm_unique_id(uint8_t id[ULLM_CUDA_COMM_ID_BYTES], ullm_cuda_error_sink_t *error_sink);

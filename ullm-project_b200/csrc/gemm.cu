@@ -597,6 +597,78 @@ size_t gemm_scratch_bytes(const LinearArgs &a) {
   return bytes;
 }
 
+// ---- allocation-free variant ---------------------------------------------------------------------
+// Staging area of the allocation-free entry point.  `g_static_scratch` names a host-side shadow in
+// host code, never a device address: the address is looked up once per device below.
+static __device__ __align__(256) uint8_t g_static_scratch[ULLM_CUDA_STATIC_SCRATCH_BYTES];
+
+static cudaError_t static_scratch_address(int device, uint8_t **out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static uint8_t *address[kMaxDevices] = {};
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> g(mu);
+  if (address[device] == nullptr) {
+    // the caller has made `device` current (begin_op); the symbol resolves per device
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    address[device] = static_cast<uint8_t *>(p);
+  }
+  *out = address[device];
+  return cudaSuccess;
+}
+
+int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
+  *err = cudaSuccess;
+  if (a.epilogue != ULLM_CUDA_EPILOGUE_NONE) return -2;
+  const bool needs_x = a.prologue != ULLM_CUDA_PROLOGUE_NONE || a.x_dtype != ULLM_CUDA_DTYPE_BF16 ||
+                       reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (a.x_stride * 2) % 16 != 0;
+  if (needs_x && (uint64_t)a.m * a.k * 2 > ULLM_CUDA_STATIC_SCRATCH_BYTES) return -2;
+  int launches = 0;
+  const void *x = a.x;
+  uint64_t x_stride = a.x_stride;
+  if (needs_x) {
+    uint8_t *scratch = nullptr;
+    *err = static_scratch_address(ctx->device, &scratch);
+    if (*err != cudaSuccess) return -1;
+    __nv_bfloat16 *xb = reinterpret_cast<__nv_bfloat16 *>(scratch);
+    prologue_kernel<<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, xb);
+    *err = cudaGetLastError();
+    if (*err != cudaSuccess) return -1;
+    ++launches;
+    x = xb;
+    x_stride = a.k;
+  }
+  GemmParams p{};
+  p.w = a.w;
+  p.scales = a.scales;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.flags = ctx->device_flags;
+  p.y = a.y;
+  p.y_stride = a.y_stride;
+  p.y_dtype = a.y_dtype;
+  const int tt = tile_tokens(a.m, a.encoding);
+  CUtensorMap map;
+  if (!make_x_map(&map, x, a.m, a.k, x_stride, (uint32_t)tt)) {
+    *err = cudaErrorInvalidValue;
+    return -1;
+  }
+  if (a.encoding == AQ4) {
+    *err = tt == 32 ? launch_tile<AQ4, 32>(stream, map, p) : tt == 64 ? launch_tile<AQ4, 64>(stream, map, p)
+                                                                      : launch_tile<AQ4, 128>(stream, map, p);
+  } else {
+    *err = tt == 32    ? launch_tile<FP8, 32>(stream, map, p)
+           : tt == 64  ? launch_tile<FP8, 64>(stream, map, p)
+           : tt == 128 ? launch_tile<FP8, 128>(stream, map, p)
+                       : launch_tile<FP8, 256>(stream, map, p);
+  }
+  if (*err != cudaSuccess) return -1;
+  return launches + 1;
+}
+
 int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
   int launches = 0;
   const bool needs_x = a.prologue != ULLM_CUDA_PROLOGUE_NONE || a.x_dtype != ULLM_CUDA_DTYPE_BF16 ||

@@ -236,6 +236,9 @@ int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, 
 bool matvec_supports(const LinearArgs &a, const char **why);
 
 int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+// The GEMM path with its activation staging area in a fixed file-scope device array (no allocation).
+// Returns kernels launched, -1 with *err set, or -2 when the arguments do not fit the array.
+int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
 // Scratch bytes launch_gemm needs for these arguments, and a way to reserve them ahead of
 // time (the scratch may not grow while a stream is being captured).
 size_t gemm_scratch_bytes(const LinearArgs &a);

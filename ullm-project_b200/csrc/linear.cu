@@ -148,6 +148,36 @@ ullm_status_t ullm_cuda_linear_enqueue(ullm_cuda_queue_t *queue, const ullm_cuda
   ULLM_ENTRY_END("linear enqueue")
 }
 
+ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_queue_t *queue,
+                                                      const ullm_cuda_linear_desc_t *desc,
+                                                      ullm_cuda_error_sink_t *error_sink) {
+  // Allocation-free: the activation staging area is a fixed device array inside the library.
+  // The first call on a device resolves that array's address (do it outside stream capture).
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "linear descriptor is null");
+  Queue *q = nullptr;
+  st = begin_op(queue, sink, &q);
+  if (st != ULLM_STATUS_OK) return st;
+  Resolved r;
+  st = resolve_linear(desc, q->ctx, true, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  const char *why = "";
+  if (!gemm_supports(q->ctx, r.args, &why)) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "gemm: %s", why);
+  cudaError_t e = cudaSuccess;
+  const int launched = launch_gemm_static_scratch(q->ctx, q->stream, r.args, &e);
+  if (launched == -2)
+    return errorf(sink, ULLM_STATUS_UNSUPPORTED,
+                  "the allocation-free linear needs M*K*2 <= %llu bytes of staging (got %llu) and no SwiGLU epilogue",
+                  (unsigned long long)ULLM_CUDA_STATIC_SCRATCH_BYTES,
+                  (unsigned long long)r.args.m * r.args.k * 2ull);
+  if (launched < 0) return cuda_error(sink, e, "allocation-free linear launch");
+  return end_launch(q, sink, "allocation-free linear launch", static_cast<uint64_t>(launched));
+  ULLM_ENTRY_END("linear enqueue (static scratch)")
+}
+
 ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
                                       ullm_cuda_completion_t **completion,
                                       ullm_cuda_error_sink_t *error_sink) {

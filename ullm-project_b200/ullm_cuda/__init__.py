@@ -283,6 +283,12 @@ class Queue(_Handle):
     def linear_enqueue(self, desc: abi.LinearDesc):
         _call("ullm_cuda_linear_enqueue", self._h, C.byref(desc))
 
+    def linear_enqueue_static_scratch(self, desc: abi.LinearDesc):
+        """The GEMM-path linear without any device allocation: its activation staging area is a fixed
+        array inside the library (limits: M*K*2 <= abi.STATIC_SCRATCH_BYTES, no SwiGLU epilogue).
+        Calls on one device share that array, so they must not overlap on the GPU."""
+        _call("ullm_cuda_linear_enqueue_static_scratch", self._h, C.byref(desc))
+
     def linear_submit(self, desc: abi.LinearDesc) -> Completion:
         c = Completion()
         _call("ullm_cuda_linear_submit", self._h, C.byref(desc), C.byref(c._h))

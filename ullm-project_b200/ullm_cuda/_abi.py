@@ -29,6 +29,7 @@ STACK_FLAG_NO_GRAPH = 1
 STACK_FLAG_KEEP_ACTIVATIONS = 2
 LINEAR_QKV, LINEAR_O, LINEAR_GATE_UP, LINEAR_DOWN, LINEAR_LM_HEAD = 0, 1, 2, 3, 4
 COMM_ID_BYTES = 128
+STATIC_SCRATCH_BYTES = 8 << 20
 
 u32, u64, vp = C.c_uint32, C.c_uint64, C.c_void_p
 
@@ -136,6 +137,7 @@ SIGNATURES = {
     "ullm_cuda_linear_supports": [P(LinearDesc), P(u32), SINK],
     "ullm_cuda_linear_enqueue": [vp, P(LinearDesc), SINK],
     "ullm_cuda_linear_submit": [vp, P(LinearDesc), P(vp), SINK],
+    "ullm_cuda_linear_enqueue_static_scratch": [vp, P(LinearDesc), SINK],
     "ullm_cuda_comm_unique_id": [P(C.c_uint8), SINK],
     "ullm_cuda_comm_create": [vp, P(C.c_uint8), u32, u32, P(vp), SINK],
     "ullm_cuda_comm_all_reduce": [vp, vp, Tensor, u64, u32, SINK],
