@@ -300,6 +300,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; the line says so)")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-matvec figures and the CPU baseline")
+    ap.add_argument("--nccl-only", action="store_true", help="sum over ranks with ncclAllReduce instead of the fused peer-memory push")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -342,7 +343,8 @@ def main():
         comm = U.Comm(ctx, box[0], rank, world)
 
     B = args.batch
-    stack = U.Stack(ctx, q, shape, enc_id, max_tokens=B, seed=SEED, tp_rank=rank, tp_size=world, comm=comm)
+    stack = U.Stack(ctx, q, shape, enc_id, max_tokens=B, seed=SEED, tp_rank=rank, tp_size=world, comm=comm,
+                    flags=U.STACK_FLAG_NCCL_ONLY if args.nccl_only else 0)
     xin = ctx.alloc(B * shape.hidden * 2)
     yout = ctx.alloc(B * stack.local_vocab * 2)
     q.synth_activations(SEED, 77, 0, B * shape.hidden, xin.at(0))

@@ -358,6 +358,7 @@ typedef struct ullm_cuda_stack_desc_t {
 
 #define ULLM_CUDA_STACK_FLAG_NO_GRAPH UINT32_C(1) /* launch kernels directly instead of replaying a graph */
 #define ULLM_CUDA_STACK_FLAG_KEEP_ACTIVATIONS UINT32_C(2) /* one activation set per layer, readable after a step */
+#define ULLM_CUDA_STACK_FLAG_NCCL_ONLY UINT32_C(4) /* sum over ranks with ncclAllReduce even for decode steps */
 
 ULLM_CUDA_API ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_queue_t *queue,
                                      ullm_cuda_comm_t *comm, const ullm_cuda_stack_desc_t *desc,

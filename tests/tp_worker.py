@@ -34,8 +34,9 @@ def main():
     xb = o.f32_to_bf16_bits(x).reshape(m, shape.hidden)
     ref = o.stack_reference(seed, enc_name, shape.layers, shape.hidden, shape.q_heads, shape.kv_heads, shape.head_dim,
                             shape.ffn, shape.vocab, x)
+    nccl_only = len(sys.argv) > 3 and sys.argv[3] == "nccl"
     st = U.Stack(ctx, q, shape, enc, max_tokens=m, tp_rank=rank, tp_size=world, comm=comm,
-                 flags=U.STACK_FLAG_KEEP_ACTIVATIONS)
+                 flags=U.STACK_FLAG_KEEP_ACTIVATIONS | (U.STACK_FLAG_NCCL_ONLY if nccl_only else 0))
     y = None
     for _ in range(2):
         y = o.bf16_bits_to_f32(st.step_host(xb))
@@ -45,8 +46,9 @@ def main():
     err = float(np.sqrt(np.mean((y - mine) ** 2)) / np.sqrt(np.mean(mine ** 2)))
     assert err < 0.02, err
     _, launches = st.stats()
-    if m <= 8:  # matvec path: one kernel per linear + one all-reduce after O and after down
-        assert launches == shape.layers * 4 + 1 + shape.layers * 2
+    if m <= 8:  # matvec path: one kernel per linear; the sum over ranks is fused into them (peer-memory
+        # push), or one ncclAllReduce after O and after down when peer mapping is unavailable / switched off
+        assert launches in (shape.layers * 4 + 2, shape.layers * 4 + 1 + shape.layers * 2)  # push: + the step tick
     # the first row-parallel sum, checked at the stated tolerance: O(qkv) summed over ranks
     info = st.linear_info(0, U.LINEAR_O)
     o_sum = q.download(info.last_output, (m, shape.hidden), np.float32)

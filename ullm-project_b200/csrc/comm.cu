@@ -9,6 +9,8 @@
 
 #include <dlfcn.h>
 
+#include <vector>
+
 namespace ullm {
 
 namespace {
@@ -21,8 +23,11 @@ typedef struct {
 typedef int ncclResult_t;
 constexpr int kNcclSum = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9;
 
+constexpr int kNcclChar = 0;
+
 struct Nccl {
   void *handle = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -52,6 +57,7 @@ Nccl &nccl() {
     ULLM_SYM(GetUniqueId, "ncclGetUniqueId")
     ULLM_SYM(CommInitRank, "ncclCommInitRank")
     ULLM_SYM(AllReduce, "ncclAllReduce")
+    ULLM_SYM(AllGather, "ncclAllGather")
     ULLM_SYM(CommDestroy, "ncclCommDestroy")
     ULLM_SYM(GetErrorString, "ncclGetErrorString")
     ULLM_SYM(GetVersion, "ncclGetVersion")
@@ -68,12 +74,88 @@ struct Comm {
   Context *ctx = nullptr;
   ncclComm_t comm = nullptr;
   uint32_t rank = 0, size = 1;
+  // Symmetric peer memory (same size and layout on every rank), mapped with CUDA IPC:
+  // sym[r] is rank r's buffer as seen from this process; sym[rank] is the local one.
+  uint8_t *sym[kMaxPeers] = {};
+  size_t sym_bytes = 0;
+  bool p2p = false;
 };
 
 Comm *as_comm(const ullm_cuda_comm_t *h) {
   Comm *c = checked<Comm>(h);
   return (c && c->magic == kMagicComm) ? c : nullptr;
 }
+// Collective over the communicator: every rank allocates `bytes` of zeroed device memory and
+// maps every peer's allocation (CUDA IPC, peer access over NVLink).  Returns false (and leaves
+// the communicator on NCCL only) when any step is not available.
+bool comm_sym_setup(Comm *c, size_t bytes, std::string *why) {
+  if (c->p2p && c->sym_bytes >= bytes) return true;
+  if (c->sym_bytes != 0 || c->size > (uint32_t)kMaxPeers) {
+    if (why) *why = "symmetric memory already set up with a smaller size";
+    return false;
+  }
+  Nccl &n = nccl();
+  // Every rank walks through the same two all-gathers whatever happens locally, so that no rank
+  // is left waiting in a collective and all ranks reach the same verdict.
+  uint8_t *local = nullptr;
+  uint8_t *hbuf = nullptr;  // [size] IPC handles, then [size] verdict bytes
+  const size_t hsz = sizeof(cudaIpcMemHandle_t);
+  if (cudaMalloc(reinterpret_cast<void **>(&hbuf), (hsz + 16) * c->size) != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (why) *why = "device allocation failed";
+    return false;
+  }
+  uint8_t *vbuf = hbuf + hsz * c->size;
+  cudaIpcMemHandle_t mine;
+  std::memset(&mine, 0, sizeof(mine));
+  std::vector<cudaIpcMemHandle_t> all(c->size);
+  bool ok = cudaMalloc(reinterpret_cast<void **>(&local), bytes) == cudaSuccess;
+  ok = ok && cudaMemset(local, 0, bytes) == cudaSuccess;
+  ok = ok && cudaIpcGetMemHandle(&mine, local) == cudaSuccess;
+  if (!ok) std::memset(&mine, 0, sizeof(mine));
+  bool coll = cudaMemcpy(hbuf + hsz * c->rank, &mine, hsz, cudaMemcpyHostToDevice) == cudaSuccess;
+  coll = n.AllGather(hbuf + hsz * c->rank, hbuf, hsz, kNcclChar, c->comm, nullptr) == 0 && coll;
+  coll = cudaStreamSynchronize(nullptr) == cudaSuccess && coll;
+  coll = cudaMemcpy(all.data(), hbuf, hsz * c->size, cudaMemcpyDeviceToHost) == cudaSuccess && coll;
+  ok = ok && coll;
+  if (ok) {
+    c->sym[c->rank] = local;
+    for (uint32_t r = 0; r < c->size && ok; ++r) {
+      if (r == c->rank) continue;
+      bool zero = true;
+      for (size_t i = 0; i < hsz; ++i) zero = zero && reinterpret_cast<const uint8_t *>(&all[r])[i] == 0;
+      void *p = nullptr;
+      ok = !zero && cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+      c->sym[r] = static_cast<uint8_t *>(p);
+    }
+  }
+  // second round: one verdict byte per rank; peer memory is used only if every rank succeeded
+  std::vector<uint8_t> verdict(16 * c->size, 0);
+  const uint8_t my_verdict[16] = {static_cast<uint8_t>(ok ? 1 : 0)};
+  coll = cudaMemcpy(vbuf + 16 * c->rank, my_verdict, 16, cudaMemcpyHostToDevice) == cudaSuccess;
+  coll = n.AllGather(vbuf + 16 * c->rank, vbuf, 16, kNcclChar, c->comm, nullptr) == 0 && coll;
+  coll = cudaStreamSynchronize(nullptr) == cudaSuccess && coll;
+  coll = cudaMemcpy(verdict.data(), vbuf, 16 * c->size, cudaMemcpyDeviceToHost) == cudaSuccess && coll;
+  ok = ok && coll;
+  for (uint32_t r = 0; r < c->size; ++r) ok = ok && verdict[16 * r] == 1;
+  (void)cudaFree(hbuf);
+  if (!ok) {
+    (void)cudaGetLastError();
+    for (uint32_t r = 0; r < c->size; ++r)
+      if (r != c->rank && c->sym[r]) (void)cudaIpcCloseMemHandle(c->sym[r]);
+    if (local) (void)cudaFree(local);
+    for (auto &q : c->sym) q = nullptr;
+    if (why) *why = "CUDA IPC peer mapping is not available on every rank";
+    return false;
+  }
+  c->sym_bytes = bytes;
+  c->p2p = true;
+  return true;
+}
+bool comm_p2p(const Comm *c) { return c->p2p; }
+uint8_t *comm_sym_ptr(const Comm *c, uint32_t peer) { return c->sym[peer]; }
+size_t comm_sym_bytes(const Comm *c) { return c->sym_bytes; }
+
 uint32_t comm_size(const Comm *c) { return c->size; }
 uint32_t comm_rank(const Comm *c) { return c->rank; }
 
@@ -189,6 +271,13 @@ ullm_status_t ullm_cuda_comm_destroy(ullm_cuda_comm_t **comm, ullm_cuda_error_si
   registry().remove(cm);
   (void)cudaSetDevice(cm->ctx->device);
   (void)cudaDeviceSynchronize();
+  for (uint32_t r = 0; r < cm->size; ++r) {
+    if (cm->sym[r] == nullptr) continue;
+    if (r == cm->rank)
+      (void)cudaFree(cm->sym[r]);
+    else
+      (void)cudaIpcCloseMemHandle(cm->sym[r]);
+  }
   nccl().CommDestroy(cm->comm);
   cm->ctx->live_children--;
   cm->magic = 0;

@@ -214,6 +214,34 @@ inline uint64_t dtype_bytes(uint32_t dtype) {
   }
 }
 
+// ---- fused all-reduce over peer memory (decode path) -------------------------------------------
+// A row-parallel matvec writes every fp32 partial output together with a 32-bit tag as ONE 8-byte
+// store into a slot of EVERY rank's symmetric buffer (plain peer stores over NVLink; 8-byte stores
+// are single-copy atomic, so a reader that sees the tag sees the value: no fence, no flag word, no
+// atomic).  The next kernel on each rank sums the ranks' slots while it stages its activations,
+// re-reading (time-bounded) any pair whose tag is not yet the expected one.  The tag is
+// step_counter * uses_per_step + use + 1, where a one-thread kernel bumps step_counter once per
+// step; two slot sets alternate per use of a site so that a fast rank never overwrites what a slow
+// rank is still reading.
+constexpr int kMaxPeers = 8;
+struct PushOut {       // producer side
+  uint8_t *peer_base[kMaxPeers];  // every rank's symmetric buffer as mapped here
+  uint64_t slot_off[2];           // slot sets (pairs of {value, tag}), chosen by use parity
+  uint64_t slot_stride;           // bytes between two ranks' slots
+  const uint32_t *step_counter;   // local
+  uint32_t uses_per_step, use;    // this site's position in the step's sequence of uses
+  uint32_t tp = 0, rank = 0;      // tp == 0: disabled
+};
+struct PushIn {        // consumer side
+  const uint8_t *local_base;
+  uint64_t slot_off[2];
+  uint64_t slot_stride;
+  const uint32_t *step_counter;
+  uint32_t uses_per_step, use;
+  float *reduced_out;             // optional: CTA 0 also stores the summed rows here
+  uint32_t tp = 0;
+};
+
 // ---- internal launchers (raw device pointers; arguments already validated) -----
 
 struct LinearArgs {
@@ -229,6 +257,8 @@ struct LinearArgs {
   uint32_t prologue = 0;
   uint32_t epilogue = 0;
   float rms_eps = 1e-5f;
+  PushOut push_out{};  // matvec only: write the fp32 output into every rank's slot instead of y
+  PushIn push_in{};    // matvec only: the input is the sum of the ranks' slots
 };
 
 // returns the number of kernels launched, or -1 after setting *err
@@ -263,6 +293,10 @@ void launch_dequantize(cudaStream_t s, uint32_t encoding, const uint8_t *values,
 
 // comm internals used by the stack
 struct Comm;
+bool comm_sym_setup(Comm *c, size_t bytes, std::string *why);
+bool comm_p2p(const Comm *c);
+uint8_t *comm_sym_ptr(const Comm *c, uint32_t peer);
+size_t comm_sym_bytes(const Comm *c);
 Comm *as_comm(const ullm_cuda_comm_t *h);
 cudaError_t comm_all_reduce_raw(Comm *c, cudaStream_t s, void *data, uint64_t count, uint32_t dtype,
                                 std::string *why);

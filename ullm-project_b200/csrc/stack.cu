@@ -22,6 +22,7 @@
 #include "internal.hpp"
 
 #include <chrono>
+#include <cstdlib>
 #include <map>
 #include <new>
 #include <thread>
@@ -63,11 +64,20 @@ struct Stack {
   std::map<uint32_t, cudaGraphExec_t> graphs;
   std::map<uint32_t, cudaGraph_t> graph_defs;
   uint64_t launches_per_step = 0;
+  // fused all-reduce over peer memory (decode path): a ring of sites inside the symmetric buffer
+  bool push = false;
+  static constexpr uint32_t kRing = 4;
+  uint64_t ring_slot_off[kRing][2] = {};
+  uint64_t step_counter_off = 0;        // local word bumped once per step
+  uint64_t slot_stride = 0;
+  uint32_t sites = 0;                   // row-parallel linears per step
 };
 
 namespace {
 
 uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+__global__ void step_tick_kernel(uint32_t *counter) { *counter += 1u; }
 
 uint64_t values_bytes(uint32_t enc, uint64_t n, uint64_t k) { return enc == ULLM_CUDA_ENCODING_AQ4 ? n * (k / 2) : n * k; }
 uint64_t scales_bytes(uint32_t enc, uint64_t n, uint64_t k) {
@@ -173,8 +183,53 @@ LinearArgs make_args(const Stack *st, const StackLinear &L, uint32_t m) {
 int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) {
   cudaStream_t s = st->queue->stream;
   int64_t launches = 0;
+  const uint32_t tp = st->desc.tp_size;
+  const bool push = st->push && m <= 8;  // the matvec path carries the fused all-reduce
+  if (push) {
+    // one tick per step: every tag of this step derives from the counter
+    step_tick_kernel<<<1, 1, 0, s>>>(reinterpret_cast<uint32_t *>(comm_sym_ptr(st->comm, st->desc.tp_rank) + st->step_counter_off));
+    *err = cudaGetLastError();
+    if (*err != cudaSuccess) {
+      if (why) *why = "step tick launch failed";
+      return -1;
+    }
+    ++launches;
+  }
+  uint32_t site = 0;                      // row-parallel linears seen so far in this step
+  bool consume = false;                   // the previous linear pushed: this one sums the slots
   for (const StackLinear &L : st->linears) {
-    const LinearArgs a = make_args(st, L, m);
+    LinearArgs a = make_args(st, L, m);
+    if (push && (consume || L.row_parallel)) {
+      uint8_t *local = comm_sym_ptr(st->comm, st->desc.tp_rank);
+      const uint32_t *counter = reinterpret_cast<const uint32_t *>(local + st->step_counter_off);
+      auto uses_of = [&](uint32_t r) { return (st->sites - r + Stack::kRing - 1) / Stack::kRing; };
+      if (consume) {
+        const uint32_t r = (site - 1) % Stack::kRing;
+        a.push_in.local_base = local;
+        a.push_in.slot_off[0] = st->ring_slot_off[r][0];
+        a.push_in.slot_off[1] = st->ring_slot_off[r][1];
+        a.push_in.slot_stride = st->slot_stride;
+        a.push_in.step_counter = counter;
+        a.push_in.uses_per_step = uses_of(r);
+        a.push_in.use = (site - 1) / Stack::kRing;
+        a.push_in.reduced_out = const_cast<float *>(static_cast<const float *>(a.x));  // keeps the sum readable
+        a.push_in.tp = tp;
+      }
+      if (L.row_parallel) {
+        const uint32_t r = site % Stack::kRing;
+        for (uint32_t q = 0; q < tp; ++q) a.push_out.peer_base[q] = comm_sym_ptr(st->comm, q);
+        a.push_out.slot_off[0] = st->ring_slot_off[r][0];
+        a.push_out.slot_off[1] = st->ring_slot_off[r][1];
+        a.push_out.slot_stride = st->slot_stride;
+        a.push_out.step_counter = counter;
+        a.push_out.uses_per_step = uses_of(r);
+        a.push_out.use = site / Stack::kRing;
+        a.push_out.tp = tp;
+        a.push_out.rank = st->desc.tp_rank;
+      }
+    }
+    consume = push && L.row_parallel;
+    if (L.row_parallel) ++site;
     const char *reason = "";
     int n;
     if (matvec_supports(a, &reason)) {
@@ -191,7 +246,10 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
       return -1;
     }
     launches += n;
-    if (L.row_parallel && st->desc.tp_size > 1) {
+    // Measurement aid: ULLM_CUDA_DEBUG_SKIP_REDUCE=1 leaves the partial sums unreduced (WRONG
+    // results) so that a step can be timed without any communication.
+    static const bool skip_reduce = std::getenv("ULLM_CUDA_DEBUG_SKIP_REDUCE") != nullptr;
+    if (L.row_parallel && st->desc.tp_size > 1 && !push && !skip_reduce) {
       std::string nccl_why;
       *err = comm_all_reduce_raw(st->comm, s, a.y, static_cast<uint64_t>(m) * L.y_stride, ULLM_CUDA_DTYPE_F32, &nccl_why);
       if (*err != cudaSuccess) {
@@ -440,6 +498,23 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   }
   (void)cudaMemsetAsync(S->acts->ptr, 0, aoff, q->stream);
   (void)cudaMemsetAsync(S->io->ptr, 0, S->io->size, q->stream);
+
+  // ---- symmetric peer memory for the fused all-reduce (collective: every rank gets here) --------
+  if (t > 1 && !(d.flags & ULLM_CUDA_STACK_FLAG_NCCL_ONLY)) {
+    const uint64_t mt8 = mt < 8 ? mt : 8;  // only steps of up to 8 tokens use it
+    S->slot_stride = align_up(mt8 * d.hidden * 8, 256);  // {value, tag} pairs
+    S->sites = 2 * d.layers;
+    uint64_t off = 0;
+    for (uint32_t r = 0; r < Stack::kRing; ++r)
+      for (int par = 0; par < 2; ++par) {
+        S->ring_slot_off[r][par] = off;
+        off += S->slot_stride * t;
+      }
+    S->step_counter_off = off;
+    off += 256;
+    std::string why;
+    S->push = comm_sym_setup(cm, off, &why);  // false: stay on NCCL (same verdict on every rank)
+  }
 
   // ---- reserve the GEMM path's scratch for the largest step (it cannot grow during capture) ----
   if (d.max_tokens > 8) {

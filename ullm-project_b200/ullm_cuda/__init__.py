@@ -22,7 +22,7 @@ from . import _abi as abi
 from ._abi import (EPILOGUE_NONE, EPILOGUE_SWIGLU, DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_F8E4M3FN, DTYPE_I8, DTYPE_U8, ENCODING_AQ4,  # noqa: F401
                    ENCODING_FP8_CHANNEL, ENCODING_NVFP4, KERNEL_AUTO, KERNEL_GEMM, KERNEL_MATVEC, LINEAR_DOWN,
                    LINEAR_GATE_UP, LINEAR_LM_HEAD, LINEAR_O, LINEAR_QKV, PROLOGUE_NONE, PROLOGUE_RMSNORM,
-                   PROLOGUE_SWIGLU, STACK_FLAG_KEEP_ACTIVATIONS, STACK_FLAG_NO_GRAPH)
+                   PROLOGUE_SWIGLU, STACK_FLAG_KEEP_ACTIVATIONS, STACK_FLAG_NCCL_ONLY, STACK_FLAG_NO_GRAPH)
 
 ERROR_CAPACITY = 512
 

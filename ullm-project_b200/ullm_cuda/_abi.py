@@ -27,6 +27,7 @@ EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 KERNEL_AUTO, KERNEL_MATVEC, KERNEL_GEMM = 0, 1, 2
 STACK_FLAG_NO_GRAPH = 1
 STACK_FLAG_KEEP_ACTIVATIONS = 2
+STACK_FLAG_NCCL_ONLY = 4
 LINEAR_QKV, LINEAR_O, LINEAR_GATE_UP, LINEAR_DOWN, LINEAR_LM_HEAD = 0, 1, 2, 3, 4
 COMM_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 8 << 20
