@@ -218,7 +218,8 @@ inline uint64_t dtype_bytes(uint32_t dtype) {
 // A row-parallel matvec writes every fp32 partial output together with a 32-bit tag as ONE 8-byte
 // store into a slot of EVERY rank's symmetric buffer (plain peer stores over NVLink; 8-byte stores
 // are single-copy atomic, so a reader that sees the tag sees the value: no fence, no flag word, no
-// atomic).  The next kernel on each rank sums the ranks' slots while it stages its activations,
+// atomic).  The next kernel on each rank sums the ranks' slots while it stages its activations
+// (each CTA a share, published with the same tag to a local buffer all CTAs then read),
 // re-reading (time-bounded) any pair whose tag is not yet the expected one.  The tag is
 // step_counter * uses_per_step + use + 1, where a one-thread kernel bumps step_counter once per
 // step; two slot sets alternate per use of a site so that a fast rank never overwrites what a slow
@@ -236,6 +237,9 @@ struct PushIn {        // consumer side
   const uint8_t *local_base;
   uint64_t slot_off[2];
   uint64_t slot_stride;
+  uint8_t *reduced;               // local {sum, tag} pairs: each CTA sums a 1/grid share of the ranks' slots
+                                  // into it, then every CTA stages from it (so the ranks' slots are read once
+                                  // per GPU, not once per CTA)
   const uint32_t *step_counter;
   uint32_t uses_per_step, use;
   float *reduced_out;             // optional: CTA 0 also stores the summed rows here

@@ -92,51 +92,94 @@ struct Params {
   uint32_t *flags;  // device view of the context's error words
 };
 
+// Reads N 16-byte words of {value, tag, value, tag} until every tag equals `want` (time-bounded:
+// on expiry the context is flagged and whatever was read is used).
+template <int N>
+__device__ __forceinline__ void poll_pairs(const Params &p, const uint4 *src, uint32_t want, uint4 (&q)[N]) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
+                   : "l"(src + i)
+                   : "memory");
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < N; ++i) ok = ok && q[i].y == want && q[i].w == want;
+    if (ok) return;
+    if ((spin & 0x3fu) == 0x3fu) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      if (now - t0 > 20ull * 1000ull * 1000ull * 1000ull) {
+        if (p.flags != nullptr) atomicOr(p.flags, 4u);
+        return;
+      }
+    }
+  }
+}
+
+// fused all-reduce, consumer half, first stage: this CTA sums its share of the ranks' slots (pairs of
+// values, in rank order: deterministic) and publishes {sum, tag} pairs for all CTAs of this GPU.
+template <int T>
+__device__ __forceinline__ void reduce_share(const Params &p, uint32_t rows) {
+  const uint32_t use_global = *p.pi.step_counter * p.pi.uses_per_step + p.pi.use;
+  const uint32_t want = use_global + 1u;
+  const uint32_t units = rows * p.k / 2;  // one unit = two values = one 16-byte word of pairs
+  const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u];
+  for (uint32_t u = blockIdx.x + threadIdx.x * gridDim.x; u < units; u += gridDim.x * T) {
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
+      if (r < p.pi.tp) {
+        uint4 q[1];
+        poll_pairs<1>(p, reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride) + u, want, q);
+        s0 += __uint_as_float(q[0].x);
+        s1 += __uint_as_float(q[0].z);
+      }
+    }
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(reinterpret_cast<uint4 *>(p.pi.reduced) + u),
+                 "r"(__float_as_uint(s0)), "r"(want), "r"(__float_as_uint(s1)), "r"(want)
+                 : "memory");
+  }
+}
+
 // x[m][k .. k+8) (k % 8 == 0, k + 8 <= row length) as eight packed bf16 values; fp32
 // inputs are rounded to bf16 here (the op is defined on bf16 activations).
 template <int MODE>
 __device__ __forceinline__ uint4 load8_packed(const Params &p, uint32_t m, uint32_t k) {
   uint32_t w[4];
   if (MODE == kModePushIn) {
-    // fused all-reduce, consumer half: sum the ranks' fp32 partials in rank order (deterministic).
-    // Every value travels with its tag in one 8-byte word; a pair that is not there yet is re-read.
+    // fused all-reduce, consumer half, second stage: read the rank-summed values this GPU's CTAs
+    // have published as {sum, tag} pairs (see reduce_share); a pair that is not there yet is re-read.
     const uint32_t use_global = *p.pi.step_counter * p.pi.uses_per_step + p.pi.use;
     const uint32_t want = use_global + 1u;
-    const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u] + ((uint64_t)m * p.k + k) * 8;
     float v[8];
+    if (p.pi.reduced != nullptr) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.pi.reduced + ((uint64_t)m * p.k + k) * 8);
+      uint4 q[4];
+      poll_pairs<4>(p, src, want, q);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(q[i].x);
+        v[2 * i + 1] = __uint_as_float(q[i].z);
+      }
+    } else {
+      // few ranks: every CTA sums the ranks' slots itself (one stage, no local round trip)
+      const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u] + ((uint64_t)m * p.k + k) * 8;
 #pragma unroll
-    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
-      if (r < p.pi.tp) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride);
-        uint4 q[4];
-        uint64_t t0 = 0;
-        for (uint32_t spin = 0;; ++spin) {
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
-                         : "l"(src + i)
-                         : "memory");
-          bool ok = true;
+      for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
+        if (r < p.pi.tp) {
+          uint4 q[4];
+          poll_pairs<4>(p, reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride), want, q);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) ok = ok && q[i].y == want && q[i].w == want;
-          if (ok) break;
-          if ((spin & 0x3fu) == 0x3fu) {
-            uint64_t now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            if (now - t0 > 20ull * 1000ull * 1000ull * 1000ull) {  // give up: flag the context, results are void
-              if (p.flags != nullptr) atomicOr(p.flags, 4u);
-              break;
-            }
+          for (int i = 0; i < 4; ++i) {
+            v[2 * i] += __uint_as_float(q[i].x);
+            v[2 * i + 1] += __uint_as_float(q[i].z);
           }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          v[2 * i] += __uint_as_float(q[i].x);
-          v[2 * i + 1] += __uint_as_float(q[i].z);
         }
       }
     }
@@ -279,6 +322,7 @@ template <int M, int T, int CACHE, uint32_t ENC, int MODE>
 __device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq, float *red) {
   const uint32_t tid = threadIdx.x;
   const uint32_t nchunks = p.k / 8, padded = p.k_pad / 8;
+  if (MODE == kModePushIn && p.pi.reduced != nullptr) reduce_share<T>(p, M);
   const bool rms = p.prologue == ULLM_CUDA_PROLOGUE_RMSNORM;
   const bool cached = rms && nchunks <= (uint32_t)(CACHE * T);
   uint4 cache[M][CACHE];
