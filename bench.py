@@ -168,7 +168,7 @@ def run_reference(args, shape, enc):
     print(json.dumps(line), flush=True)
 
 
-def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps):
+def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps, kernel=None):
     """Time per launch of one matvec shape over enough distinct weight copies to exceed 2x L2,
     replayed as one graph (so the figure is HBM, not L2, and launch gaps are the graph's)."""
     vb, sb = U.weight_bytes(enc_id, n, k)
@@ -183,7 +183,9 @@ def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps):
         wd = U.weight_desc(enc_id, n, k, v.at(0), s.at(0))
         q.quantize(src.at(0), wd)
         bufs += [v, s]
-        descs.append(U.linear_desc(wd, m, xb.at(0), yb.at(0), kernel=U.KERNEL_MATVEC))
+        descs.append(U.linear_desc(wd, m, xb.at(0), yb.at(0), kernel=U.KERNEL_MATVEC if kernel is None else kernel))
+    q.linear_enqueue(descs[0])  # any scratch the kernel needs exists before the capture
+    q.synchronize()
     q.capture_begin()
     for d in descs:
         q.linear_enqueue(d)
@@ -273,12 +275,14 @@ def run_single_matvec(U, args):
     ctx = U.Context(0)
     q = ctx.queue()
     enc_id = U.ENCODING_AQ4 if args.enc == "aq4" else U.ENCODING_FP8_CHANNEL
-    r = time_matvec_extra(U, ctx, q, enc_id, args.n, args.k, args.batch, reps=max(args.steps, 1))
+    kernel = {"auto": U.KERNEL_AUTO, "matvec": U.KERNEL_MATVEC, "gemm": U.KERNEL_GEMM}[args.kernel]
+    r = time_matvec_extra(U, ctx, q, enc_id, args.n, args.k, args.batch, reps=max(args.steps, 1), kernel=kernel)
     peak, peak_src = peaks()
     print(json.dumps({
         "metric": "quantised matvec HBM GB/s", "value": r["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": 3, "ms_per_step": r["us_per_launch"] * r["weight_copies"] / 1e3, "higher_is_better": True,
-        "config": {"workload": f"{args.enc} matvec M={args.batch} N={args.n} K={args.k}", "weight_copies": r["weight_copies"]},
+        "config": {"workload": f"{args.enc} matvec M={args.batch} N={args.n} K={args.k}", "weight_copies": r["weight_copies"],
+                   "kernel": args.kernel},
         "roofline": {"bound": "hbm", "achieved": r["gbs"], "peak": peak, "unit": "GB/s", "frac": r["gbs"] / peak,
                      "traffic": None, "peak_source": peak_src, "us_per_launch": r["us_per_launch"],
                      "algorithmic_bytes": r["algorithmic_bytes"]},
@@ -295,6 +299,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS) + ["matvec", "gemm"])
     ap.add_argument("--enc", default="fp8", choices=["fp8", "aq4"], help="matvec workload: weight encoding")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "matvec", "gemm"],
+                    help="matvec workload: kernel behind the linear op (auto: by token count)")
     ap.add_argument("--n", type=int, default=57344, help="matvec workload: output channels")
     ap.add_argument("--k", type=int, default=8192, help="matvec workload: reduction length")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

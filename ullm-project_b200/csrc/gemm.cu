@@ -1,28 +1,41 @@
 // Prefill / batched-decode GEMM: y[M,N] = prologue(x)[M,K] . W'[N,K]^T with the AQ4 / FP8
-// dequantisation fused into the main loop, on the 5th-generation tensor cores
-// (tcgen05.mma, accumulators in tensor memory).
+// weights fed to the 5th-generation tensor cores AS STORED (tcgen05.mma kind::f8f6f4, e4m3 x e4m3
+// -> f32 accumulators in tensor memory).
 //
 // The reference has no GEMM (hipBLASLt appears only as a planned dependency,
 // docs/compatibility/amd-gpu.md:96-102); this is the tensor-core half of the quantised
 // linear op selected by shape (docs/architecture/runtime.md:83-91).
 //
-// Orientation ("swap AB"): the WEIGHT rows are the 128-row M side of the MMA and the TOKENS
-// are its N side (tile of TT <= 256 tokens).  Consequences:
-//   * a weight element is dequantised once per (128 rows x TT tokens) tile, i.e. M/TT times;
-//   * the per-output-channel (FP8) or per-group (AQ4) scale is a per-LANE scalar of the
-//     accumulator, so the epilogue thread that owns lane n applies it without any lookup;
-//   * small token counts (batched decode) simply use a narrow N.
-// One CTA per SM computes one 128 x TT tile; warp roles:
-//   warp 0      TMA: activation tiles [TT x 64] bf16, 128-byte swizzle, completion on an mbarrier
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (kind::f16, bf16 x bf16 -> f32)
-//   warps 2-9   weight producers: two threads per row n0 + r stream it from global memory (16-byte
-//               loads, four to eight k-tiles ahead), convert to EXACT bf16 (e4m3 -> bf16; 4-bit q -> bf16
-//               integer) and write the K-major, 128-byte-swizzled A tile the MMA reads
-//   warps 10-17 epilogue: tcgen05.ld, scale, convert, store
-// FP8: all of K accumulates in one tensor-memory buffer; scale[n] is applied once at the end.
-// AQ4: products of bf16 activations with integers -7..7 are exact, so a 128-deep group is
-// accumulated unscaled, drained, and added into fp32 registers as scale[n,g] * partial; two
-// accumulator buffers ping-pong so that draining overlaps the next group's MMAs.
+// Number formats.  The tensor core multiplies e4m3 by e4m3 exactly and adds in fp32, so both
+// operands are brought to e4m3 without losing bits:
+//   * FP8 weights are e4m3 already: TMA moves the stored bytes straight into the swizzled operand
+//     tile, no thread touches them.  scale[n] is applied once to the finished accumulator.
+//   * An AQ4 weight q = u - 8 (-8..7) becomes the e4m3 byte sign | |q|, which IS the number
+//     q * 2^-9 (the subnormals and the first binade of e4m3 are one linear ramp): about 1.6 integer
+//     instructions per weight, shared memory to shared memory.
+//   * A bf16 activation has 8 significant bits, e4m3 has 4: x * 2^p = hi + lo with hi the e4m3
+//     rounding of the scaled value and lo the e4m3 rounding of the rest (exact whenever the
+//     scaled |x| >= 2^-2; p is chosen per token so that the row's largest magnitude lands in
+//     [128, 256), so only elements 2^-9 and more below the row maximum lose anything, and then
+//     less than 2^-18 of that maximum).  Two MMAs per k-slice, A . hi and A . lo, add into the
+//     same accumulator: twice the instructions at twice the bf16 rate.
+//
+// Orientation ("swap AB"): the WEIGHT rows are the 128-row M side of the MMA and the TOKENS are
+// its N side (tile of TT = 16..256 tokens), so the per-channel / per-group scale is a per-LANE
+// scalar of the accumulator and a small token count just uses a narrow N.
+// CTAs are persistent (one per SM) and walk a share of all (tile, k-block) work; a tile is 128 or 256
+// weight rows x TT tokens, a k-block 128 k.  Warp roles:
+//   warp 0      TMA: per k-block the FP8 weight tile [128 x 128 B] and the two activation planes
+//               [TT x 128 B] each, 128-byte swizzle, completion on an mbarrier
+//   warp 1      owns tensor memory; one lane issues tcgen05.mma
+//   warp 2      AQ4 only, TMA: packed nibble tiles [128 x 64 B] into a ring of their own
+//   warps 4-7   AQ4 only: nibble tile -> e4m3 operand tile (shared memory to shared memory)
+//   warps 8-15  epilogue: tcgen05.ld, scales, store (or split-K partial + last-arriver sum)
+// FP8: all k-blocks accumulate in one tensor-memory buffer.  AQ4: one buffer per 128-deep scale
+// group, two or four in rotation, drained into fp32 registers as scale[n,g] * partial.
+// Accumulators are double-buffered in tensor memory, so the epilogue of one tile overlaps the MMAs of
+// the next.  A tile whose k-blocks fall into several CTAs' shares is finished by the CTA that arrives
+// last at the tile's counter, adding the fp32 partials in a fixed order (deterministic).
 // Every mbarrier wait is bounded in time; on expiry the kernel flags the context and unwinds
 // (tensor memory is always released).
 #include "internal.hpp"
@@ -32,28 +45,39 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 namespace ullm {
 
 namespace {
 
 constexpr uint32_t AQ4 = ULLM_CUDA_ENCODING_AQ4;
 constexpr uint32_t FP8 = ULLM_CUDA_ENCODING_FP8_CHANNEL;
-constexpr int BM = 128;  // weight rows per tile (MMA M)
-constexpr int BK = 64;   // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kProducerWarps = 8;
-constexpr int kProducerWarp0 = 2, kEpilogueWarp0 = kProducerWarp0 + kProducerWarps;
-constexpr int kThreads = (kEpilogueWarp0 + 8) * 32;
+constexpr int BM = 128;   // weight rows per tile (MMA M)
+constexpr int BKB = 128;  // k per k-block: 128 e4m3 bytes = one 128-byte swizzle row = one AQ4 scale group
+constexpr int kConvWarp0 = 4, kConvWarps = 4, kEpiWarp0 = 8, kEpiWarps = 8;
+constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
+constexpr uint32_t A_BYTES = BM * BKB;        // e4m3 operand tile
+constexpr uint32_t RAW_BYTES = BM * BKB / 2;  // packed nibble tile
+constexpr int MAX_STAGES = 8, MAX_RAW = 8;
 constexpr uint32_t kFlagGemmWait = 2u;
 constexpr uint64_t kWaitLimitNs = 20ull * 1000ull * 1000ull * 1000ull;
+constexpr uint32_t kMaxCounterTiles = 1024;  // phase-2 tiles: fewer than the SM count
 
 struct GemmParams {
-  const uint8_t *w;
-  const void *scales;
+  const void *scales;      // FP8: float[n]; AQ4: half[n][k/128]
+  const float *tok_scale;  // [m] 2^-p of each token's activation planes
   void *y;
-  uint32_t m, n, k;
   uint64_t y_stride;
   uint32_t y_dtype;
-  uint32_t stages;
+  uint32_t m, n, k;
+  uint32_t stages, raw_stages;
+  uint32_t whole_rounds;    // phase 1: rounds of whole tiles, tile = round * gridDim.x + CTA, below sk_tile0
+  uint32_t sk_tile0;        // phase 2: tiles sk_tile0 .. are cut into sk_ctas ranges of k-blocks
+  uint32_t sk_ctas;
+  uint32_t m_fastest;       // tile order, see tile_origin
+  float *partial;           // [range][head, tail][row block][TT][128] fp32
+  uint32_t *tile_counters;  // one per phase-2 tile, zero between launches
   uint32_t *flags;
 };
 
@@ -121,17 +145,23 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                             uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
-// 32 lanes x 32 consecutive fp32 columns: thread l of the warp receives lane (quarter*32 + l)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+// 32 lanes x N consecutive fp32 columns: thread l of the warp receives lane (quarter*32 + l)
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -143,17 +173,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint4 ldg_stream(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory"); }
 
-// K-major, 128-byte-swizzled operand tile (rows of 64 bf16, 8-row groups 1024 bytes apart):
+// K-major, 128-byte-swizzled operand tile (rows of 128 bytes, 8-row groups 1024 bytes apart):
 // start address >> 4, leading byte offset 1 (unused with a swizzle), stride byte offset 1024 >> 4,
 // descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
@@ -162,77 +194,136 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return ((uint64_t)hi << 32) | lo;
 }
 
-// instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = tt
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int tt) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tt >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// instruction descriptor: D = f32, A = B = e4m3 (format 0), both K-major, M = 128, N = tt
+__host__ __device__ constexpr uint32_t instr_desc_e4m3(int tt) {
+  return (1u << 4) | ((uint32_t)(tt >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-// ---- weight conversion to exact bf16 ----------------------------------------------------------
-// four e4m3 codes (one word) -> two words of two bf16 each
-__device__ __forceinline__ void fp8x4_to_bf16x4(uint32_t w, uint32_t &lo, uint32_t &hi) {
-  const float2 f01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3)));
-  const float2 f23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3)));
-  // an e4m3 value has 4 significant bits: the upper half of its fp32 pattern is its exact bf16
-  lo = __byte_perm(__float_as_uint(f01.x), __float_as_uint(f01.y), 0x7632);
-  hi = __byte_perm(__float_as_uint(f23.x), __float_as_uint(f23.y), 0x7632);
+__host__ __device__ constexpr uint32_t tmem_cols(uint32_t want) {
+  uint32_t c = 32;
+  while (c < want) c *= 2;
+  return c;
 }
-// eight nibbles (one word, element 2i in the low nibble of byte i) -> four words of two bf16 integers q = u - 8
-__device__ __forceinline__ void aq4x8_to_bf16x8(uint32_t w, uint32_t (&out)[4]) {
-  const __nv_bfloat162 bias = __floats2bfloat162_rn(136.0f, 136.0f);
-  const uint32_t lo = w & 0x0f0f0f0fu;         // u of elements 0,2,4,6, one per byte
-  const uint32_t hi = (w >> 4) & 0x0f0f0f0fu;  // u of elements 1,3,5,7
-  const uint32_t t03 = __byte_perm(lo, hi, 0x5140);  // bytes u0,u1,u2,u3
-  const uint32_t t47 = __byte_perm(lo, hi, 0x7362);  // bytes u4,u5,u6,u7
-  // 0x4300 | u is the bf16 number 128 + u (exact for u < 128): widen each byte with a 0x43 high byte
-  uint32_t v[4];
-  v[0] = __byte_perm(t03, 0x43434343u, 0x4140);
-  v[1] = __byte_perm(t03, 0x43434343u, 0x4342);
-  v[2] = __byte_perm(t47, 0x43434343u, 0x4140);
-  v[3] = __byte_perm(t47, 0x43434343u, 0x4342);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v[i]), bias);
-    out[i] = *reinterpret_cast<const uint32_t *>(&q);
+
+// Work distribution.  Phase 1: whole tiles, dealt round-robin (tile = round * gridDim.x + CTA) for
+// `whole_rounds` rounds: CTAs that share operands run in step, and nothing needs fixing up.  Phase 2
+// ("stream K") balances what is left: the k-blocks of the remaining tiles form one sequence, tile after
+// tile, cut into `sk_ctas` equal ranges.  A CTA walks its range segment by segment (a segment =
+// consecutive k-blocks of one tile).  A tile inside one range is stored directly; otherwise every
+// contributor writes an fp32 partial and the one arriving last at the tile's counter adds them in range
+// order (deterministic).  A CTA has at most two partial segments: a "head" (the tile began in an
+// earlier range) and a "tail".
+struct Segment {
+  uint32_t tile, kb0, nkb, first_owner, contributors;
+  bool head;
+};
+
+struct Walker {
+  uint32_t round = 0, rounds, tiles, kb_all, sk_tile0, sk_ctas;
+  uint64_t cur = 0, end = 0, units = 0;
+  __device__ Walker(const GemmParams &p, uint32_t tiles_) {
+    kb_all = p.k / BKB;
+    tiles = tiles_;
+    rounds = p.whole_rounds;
+    sk_tile0 = p.sk_tile0;
+    sk_ctas = p.sk_ctas;
+    if (blockIdx.x < sk_ctas) {
+      units = (uint64_t)(tiles - sk_tile0) * kb_all;
+      cur = start(blockIdx.x);
+      end = start(blockIdx.x + 1);
+    }
   }
+  __device__ uint64_t start(uint32_t c) const { return (uint64_t)c * units / sk_ctas; }
+  // the range that holds unit u: the largest c with floor(c * units / sk_ctas) <= u
+  __device__ uint32_t owner(uint64_t u) const { return (uint32_t)(((u + 1) * sk_ctas - 1) / units); }
+  __device__ bool next(Segment *s) {
+    while (round < rounds) {
+      const uint32_t t = round++ * gridDim.x + blockIdx.x;
+      if (t < sk_tile0) {
+        *s = Segment{t, 0u, kb_all, blockIdx.x, 1u, false};
+        return true;
+      }
+    }
+    if (cur >= end) return false;
+    s->tile = sk_tile0 + (uint32_t)(cur / kb_all);
+    s->kb0 = (uint32_t)(cur % kb_all);
+    const uint64_t left = end - cur;
+    s->nkb = kb_all - s->kb0 < left ? kb_all - s->kb0 : (uint32_t)left;
+    if (s->nkb == kb_all) {
+      s->first_owner = blockIdx.x;
+      s->contributors = 1;
+      s->head = false;
+    } else {
+      const uint64_t t0 = (cur / kb_all) * kb_all;
+      s->first_owner = owner(t0);
+      s->contributors = owner(t0 + kb_all - 1) - s->first_owner + 1;
+      s->head = blockIdx.x > s->first_owner;
+    }
+    cur += s->nkb;
+    return true;
+  }
+};
+
+// Four bytes, each holding a nibble u = q + 8 (0..15): each becomes the e4m3 byte of q * 2^-9, that is
+// |q| with the sign in bit 7 (|q| <= 8 sits in the linear part of e4m3, where the byte value is the magnitude).
+__device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
+  const uint32_t m = (~b >> 3) & 0x01010101u;     // 1 in every byte with u < 8 (negative q)
+  const uint32_t r0 = b ^ 0x08080808u ^ (m * 15u);  // u - 8 where positive, 7 - u where negative
+  return r0 + m * 129u;                             // negative: + 1 -> 8 - u, and bit 7
 }
 
-template <uint32_t ENC, int TT>
-__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+template <uint32_t ENC, int TT, int RT>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   extern __shared__ uint8_t smem_dyn[];
-  constexpr uint32_t A_BYTES = BM * BK * 2;           // 16 KiB
-  constexpr uint32_t B_BYTES = (uint32_t)TT * BK * 2;  // TT x 128 B
-  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t RAW16 = ENC == AQ4 ? 1 : 2;  // 16-byte loads of half a row per k-tile
-  constexpr int ACC_BUFS = ENC == AQ4 ? 2 : 1;
-  constexpr uint32_t TMEM_COLS = (uint32_t)(TT * ACC_BUFS) < 32u ? 32u : (uint32_t)(TT * ACC_BUFS);
-  constexpr int MAX_STAGES = 8;
-  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 4];
+  constexpr uint32_t B_BYTES = (uint32_t)TT * BKB;  // one activation plane of the stage
+  constexpr uint32_t STAGE_BYTES = RT * A_BYTES + 2 * B_BYTES;
+  constexpr uint32_t ACC_COLS = (uint32_t)(RT * TT);  // one accumulator set: RT row blocks side by side
+  // accumulator sets in tensor memory: AQ4 one per scale group in rotation, FP8 one per segment
+  constexpr int NB = ENC == AQ4 ? (ACC_COLS > 128 ? 2 : 4) : (ACC_COLS > 256 ? 1 : 2);
+  constexpr uint32_t TMEM_COLS = tmem_cols(ACC_COLS * NB);
+  static_assert(ACC_COLS * NB <= 512, "tensor memory has 512 columns");
+  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 2 * MAX_RAW + 8];
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_flag;
+  __shared__ uint32_t last_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n0 = blockIdx.x * BM, m0 = blockIdx.y * TT;
-  const uint32_t NS = p.stages;
-  const uint32_t ktiles = p.k / BK;
+  const uint32_t NS = p.stages, RS = p.raw_stages;
+  const uint32_t tiles_n = (p.n + RT * BM - 1) / (RT * BM), tiles_m = (p.m + TT - 1) / TT;
+  auto tile_origin = [&](uint32_t tile, uint32_t *n0, uint32_t *m0) {
+    // m fastest: consecutive tiles share the weight rows (read from HBM once); n fastest: they share the tokens
+    const uint32_t tn = p.m_fastest ? tile / tiles_m : tile % tiles_n, tm = p.m_fastest ? tile % tiles_m : tile / tiles_n;
+    *n0 = tn * RT * BM;
+    *m0 = tm * TT;
+  };
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
   const uint32_t smem0 = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t raw0 = smem0 + NS * STAGE_BYTES;
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
-  auto full_a = [&](uint32_t s) { return bar0 + s * 8u; };
-  auto full_b = [&](uint32_t s) { return bar0 + (MAX_STAGES + s) * 8u; };
-  auto empty = [&](uint32_t s) { return bar0 + (2 * MAX_STAGES + s) * 8u; };
-  auto acc_full = [&](uint32_t b) { return bar0 + (3 * MAX_STAGES + b) * 8u; };
-  auto acc_empty = [&](uint32_t b) { return bar0 + (3 * MAX_STAGES + 2 + b) * 8u; };
+  auto full = [&](uint32_t s) { return bar0 + s * 8u; };                          // TMA bytes of the stage landed
+  auto a_full = [&](uint32_t s) { return bar0 + (MAX_STAGES + s) * 8u; };         // AQ4: operand tile converted
+  auto empty = [&](uint32_t s) { return bar0 + (2 * MAX_STAGES + s) * 8u; };      // the stage's MMAs are done
+  auto raw_full = [&](uint32_t s) { return bar0 + (3 * MAX_STAGES + s) * 8u; };
+  auto raw_empty = [&](uint32_t s) { return bar0 + (3 * MAX_STAGES + MAX_RAW + s) * 8u; };
+  auto acc_full = [&](uint32_t b) { return bar0 + (3 * MAX_STAGES + 2 * MAX_RAW + b) * 8u; };
+  auto acc_empty = [&](uint32_t b) { return bar0 + (3 * MAX_STAGES + 2 * MAX_RAW + 4 + b) * 8u; };
 
   if (threadIdx.x == 0) {
     abort_flag = 0u;
+    last_flag = 0u;
     for (uint32_t s = 0; s < NS; ++s) {
-      mbar_init(full_a(s), (uint32_t)kProducerWarps);  // one arrival per producer warp
-      mbar_init(full_b(s), 1u);  // the TMA thread's expect_tx
-      mbar_init(empty(s), 1u);   // tcgen05.commit
+      mbar_init(full(s), 1u);                       // the TMA thread's expect_tx
+      mbar_init(a_full(s), (uint32_t)kConvWarps);   // one arrival per converter warp
+      mbar_init(empty(s), 1u);                      // tcgen05.commit
     }
-    for (uint32_t b = 0; b < 2; ++b) {
-      mbar_init(acc_full(b), 1u);   // tcgen05.commit
-      mbar_init(acc_empty(b), 8u);  // one arrival per epilogue warp
+    for (uint32_t s = 0; s < RS; ++s) {
+      mbar_init(raw_full(s), 1u);
+      mbar_init(raw_empty(s), (uint32_t)kConvWarps);
+    }
+    for (uint32_t b = 0; b < 4; ++b) {
+      mbar_init(acc_full(b), 1u);                     // tcgen05.commit
+      mbar_init(acc_empty(b), (uint32_t)kEpiWarps);   // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -245,189 +336,328 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  Walker walk(p, tiles_n * tiles_m);
+  Segment sg;
 
   if (warp == 0) {
-    // ---- TMA: activation tiles --------------------------------------------------------
+    // ---- TMA: operand tiles -----------------------------------------------------------------
     if (lane == 0) {
+      // everything before this point overlapped the kernel that wrote the activation planes
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t slot = 0, round = 0;
-      for (uint32_t kt = 0; kt < ktiles; ++kt) {
-        if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) break;
-        mbar_expect_tx(full_b(slot), B_BYTES);
-        tma_load_2d(smem0 + slot * STAGE_BYTES + A_BYTES, &tmap_x, (int)(kt * BK), (int)m0, full_b(slot));
-        if (++slot == NS) {
-          slot = 0;
-          ++round;
+      bool ok = true;
+      while (ok && walk.next(&sg)) {
+        uint32_t n0, m0;
+        tile_origin(sg.tile, &n0, &m0);
+        for (uint32_t i = 0; i < sg.nkb; ++i) {
+          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_addr = smem0 + slot * STAGE_BYTES;
+          const int kx = (int)((sg.kb0 + i) * BKB);
+          mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_BYTES : 0u) + 2 * B_BYTES);
+          if (ENC == FP8) {
+#pragma unroll
+            for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_BYTES, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
+          }
+          tma_load_3d(a_addr + RT * A_BYTES, &tmap_x, kx, (int)m0, 0, full(slot));
+          tma_load_3d(a_addr + RT * A_BYTES + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
+          if (++slot == NS) {
+            slot = 0;
+            ++round;
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issue ----------------------------------------------------------------------
+    // ---- MMA issue ------------------------------------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(TT);
+      constexpr uint32_t idesc = instr_desc_e4m3(TT);
+      uint32_t slot = 0, round = 0, seg = 0, group = 0;
+      bool ok = true;
+      while (ok && walk.next(&sg)) {
+        uint32_t buf = 0;
+        if (ENC == FP8) {
+          buf = seg % NB;
+          const uint32_t use = seg / NB;
+          if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+        }
+        for (uint32_t i = 0; i < sg.nkb && ok; ++i) {
+          uint32_t fresh = i == 0 ? 1u : 0u;
+          if (ENC == AQ4) {
+            buf = group % NB;
+            const uint32_t use = group / NB;
+            fresh = 1u;
+            if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+            ok = ok && mbar_wait(a_full(slot), round & 1u, &abort_flag, p.flags);
+          }
+          ok = ok && mbar_wait(full(slot), round & 1u, &abort_flag, p.flags);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_BYTES, lo_addr = hi_addr + B_BYTES;
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+            const uint32_t d = tmem_base + buf * ACC_COLS + r * TT;
+#pragma unroll
+            for (int k4 = 0; k4 < BKB / 32; ++k4) {
+              // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
+              const uint64_t adesc = smem_desc_sw128(a_addr + r * A_BYTES + k4 * 32);
+              tc_mma_e4m3(d, adesc, smem_desc_sw128(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
+              tc_mma_e4m3(d, adesc, smem_desc_sw128(lo_addr + k4 * 32), idesc, 1u);
+            }
+          }
+          tc_commit(empty(slot));  // the stage may be refilled when these MMAs are done
+          if (ENC == AQ4) {
+            tc_commit(acc_full(buf));
+            ++group;
+          } else if (i + 1 == sg.nkb) {
+            tc_commit(acc_full(buf));
+          }
+          if (++slot == NS) {
+            slot = 0;
+            ++round;
+          }
+        }
+        ++seg;
+      }
+    }
+  } else if (warp == 2) {
+    // ---- AQ4: TMA of the packed nibble tiles (weights: nothing to wait for) ------------------
+    if (ENC == AQ4 && lane == 0) {
       uint32_t slot = 0, round = 0;
       bool ok = true;
-      for (uint32_t kt = 0; kt < ktiles && ok; ++kt) {
-        uint32_t acc_col = 0, first = kt == 0 ? 1u : 0u;
-        if (ENC == AQ4) {
-          const uint32_t g = kt >> 1, buf = g & 1u;  // two k-tiles per scale group of 128
-          acc_col = buf * TT;
-          first = (kt & 1u) == 0u ? 1u : 0u;
-          if (first && g >= 2) ok = mbar_wait(acc_empty(buf), ((g >> 1) - 1) & 1u, &abort_flag, p.flags);
-        }
-        ok = ok && mbar_wait(full_a(slot), round & 1u, &abort_flag, p.flags);
-        ok = ok && mbar_wait(full_b(slot), round & 1u, &abort_flag, p.flags);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t a_addr = smem0 + slot * STAGE_BYTES, b_addr = a_addr + A_BYTES;
-#pragma unroll
-        for (int k4 = 0; k4 < BK / 16; ++k4) {
-          // 16 bf16 along K = 32 bytes inside the swizzled row: advance the start address only
-          tc_mma_bf16(tmem_base + acc_col, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                      (first && k4 == 0) ? 0u : 1u);
-        }
-        tc_commit(empty(slot));  // the stage may be refilled when these MMAs are done
-        if (ENC == AQ4) {
-          if ((kt & 1u) == 1u) tc_commit(acc_full((kt >> 1) & 1u));
-        } else if (kt + 1 == ktiles) {
-          tc_commit(acc_full(0));
-        }
-        if (++slot == NS) {
-          slot = 0;
-          ++round;
-        }
-      }
-    }
-  } else if (warp < kEpilogueWarp0) {
-    // ---- weight producers: threads 2r and 2r+1 own the two halves of row n0 + r of the tile -----
-    const uint32_t pt = threadIdx.x - kProducerWarp0 * 32;
-    const uint32_t r = pt >> 1, hf = pt & 1u;
-    const uint32_t row = n0 + r;
-    const bool valid = row < p.n;
-    const uint32_t row_bytes = ENC == AQ4 ? p.k / 2 : p.k;
-    const uint8_t *src = p.w + (uint64_t)(valid ? row : 0) * row_bytes + hf * (RAW16 * 16);
-    constexpr int PF = ENC == AQ4 ? 8 : 4;  // k-tiles of raw bytes kept in registers ahead of the one being converted
-    uint4 raw[PF][RAW16];
-    auto fetch = [&](uint32_t kt, int j) {
-#pragma unroll
-      for (uint32_t i = 0; i < RAW16; ++i)
-        raw[j][i] = (valid && kt < ktiles) ? ldg_stream(src + (uint64_t)kt * (2 * RAW16 * 16) + i * 16) : make_uint4(0, 0, 0, 0);
-    };
-#pragma unroll
-    for (int j = 0; j < PF; ++j) fetch((uint32_t)j, j);
-    uint32_t slot = 0, round = 0;
-    for (uint32_t kt = 0; kt < ktiles; kt += PF) {
-#pragma unroll
-      for (int j = 0; j < PF; ++j) {
-        if (kt + j >= ktiles) break;
-        if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) goto done;
-        const uint32_t a_row = smem0 + slot * STAGE_BYTES + r * 128u;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {  // chunk c = k 8c..8c+7 of this k-tile; this thread owns c = 4*hf + i
-          const uint32_t c = 4u * hf + (uint32_t)i;
-          uint32_t o[4];
-          if (ENC == FP8) {  // 8 raw bytes = 2 words
-            const uint4 q = raw[j][i >> 1];
-            const uint32_t w0 = (i & 1) ? q.z : q.x, w1 = (i & 1) ? q.w : q.y;
-            fp8x4_to_bf16x4(w0, o[0], o[1]);
-            fp8x4_to_bf16x4(w1, o[2], o[3]);
-          } else {  // 8 nibbles = 1 word
-            const uint4 q = raw[j][0];
-            const uint32_t w = i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
-            aq4x8_to_bf16x8(w, o);
+      while (ok && walk.next(&sg)) {
+        uint32_t n0, m0;
+        tile_origin(sg.tile, &n0, &m0);
+        for (uint32_t i = 0; i < sg.nkb; ++i) {
+          if (round > 0 && !mbar_wait(raw_empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+            ok = false;
+            break;
           }
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + ((c ^ (r & 7u)) << 4)), "r"(o[0]),
-                       "r"(o[1]), "r"(o[2]), "r"(o[3])
-                       : "memory");
-        }
-        fetch(kt + j + PF, j);  // refill the register slot just consumed
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_a(slot));
-        if (++slot == NS) {
-          slot = 0;
-          ++round;
+          mbar_expect_tx(raw_full(slot), RT * RAW_BYTES);
+#pragma unroll
+          for (int r = 0; r < RT; ++r)
+            tma_load_2d(raw0 + (slot * RT + r) * RAW_BYTES, &tmap_w, (int)((sg.kb0 + i) * (BKB / 2)), (int)(n0 + r * BM),
+                        raw_full(slot));
+          if (++slot == RS) {
+            slot = 0;
+            ++round;
+          }
         }
       }
     }
-  } else {
-    // ---- epilogue: warp e covers TMEM lanes 32*(warp % 4) .. +31 and half of the token columns ----
-    const uint32_t e = warp - kEpilogueWarp0;
-    const uint32_t quarter = warp & 3u, half = e >> 2;
-    constexpr int COLS = TT / 2 < 32 ? 32 : TT / 2;  // token columns of this warp (tcgen05.ld moves 32 at a time)
-    const uint32_t row = n0 + quarter * 32 + lane;
-    const uint32_t col0 = half * COLS;
-    const bool active = col0 < (uint32_t)TT;  // TT == 32: the second half has nothing to do
-    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    auto store_chunk = [&](uint32_t c, const float (&v)[32]) {
-      // thread = output channel `row`; 32 lanes write 32 consecutive channels of one token
-      if (row >= p.n) return;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const uint32_t tok = m0 + c + i;
-        if (tok < p.m) {
-          if (p.y_dtype == ULLM_CUDA_DTYPE_F32)
-            static_cast<float *>(p.y)[(uint64_t)tok * p.y_stride + row] = v[i];
-          else
-            static_cast<__nv_bfloat16 *>(p.y)[(uint64_t)tok * p.y_stride + row] = __float2bfloat16_rn(v[i]);
-        }
-      }
-    };
-    if (ENC == FP8) {
-      if (active && mbar_wait(acc_full(0), 0u, &abort_flag, p.flags)) {
-        tc_fence_after();
-        const float sc = row < p.n ? static_cast<const float *>(p.scales)[row] : 0.0f;
-#pragma unroll 1
-        for (int c = 0; c < COLS; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + col0 + c, v);
-          tmem_ld_wait();
-          float f[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * sc;
-          store_chunk(col0 + c, f);
-        }
-      }
-    } else {
-      float acc[COLS];
-#pragma unroll
-      for (int i = 0; i < COLS; ++i) acc[i] = 0.0f;
-      const uint32_t groups = p.k / 128;
-      const __half *srow = static_cast<const __half *>(p.scales) + (uint64_t)(row < p.n ? row : 0) * groups;
-      float sc_next = row < p.n ? __half2float(srow[0]) : 0.0f;
+  } else if (warp >= kConvWarp0 && warp < kConvWarp0 + kConvWarps) {
+    // ---- AQ4: nibble tile -> e4m3 operand tile ------------------------------------------------
+    // Item (row, c): the 16 bytes c of the row's 64 = k 32c .. 32c+31.  The even elements of those 32 go
+    // to operand chunk 2c, the odd ones to chunk 2c+1; the activation planes use the same order.
+    if (ENC == AQ4) {
+      const uint32_t ct = threadIdx.x - kConvWarp0 * 32;
+      uint32_t slot = 0, round = 0, rslot = 0, rround = 0;
       bool ok = true;
-      for (uint32_t g = 0; g < groups && ok; ++g) {
-        const uint32_t buf = g & 1u;
-        const float sc = sc_next;
-        if (g + 1 < groups && row < p.n) sc_next = __half2float(srow[g + 1]);
-        ok = mbar_wait(acc_full(buf), (g >> 1) & 1u, &abort_flag, p.flags);
-        if (!ok) break;
-        tc_fence_after();
-        if (active) {
+      while (ok && walk.next(&sg)) {
+        for (uint32_t i = 0; i < sg.nkb; ++i) {
+          if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags) ||
+              (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags))) {
+            ok = false;
+            break;
+          }
 #pragma unroll
-          for (int c = 0; c < COLS; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(lane_addr + buf * TT + col0 + c, v);
-            tmem_ld_wait();
+          for (int r = 0; r < RT; ++r) {
+            uint4 q[4];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(sc, __uint_as_float(v[i]), acc[c + i]);
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr = raw0 + (rslot * RT + r) * RAW_BYTES + (ct + 128u * j) * 16u;
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
+                           : "r"(addr));
+            }
+            const uint32_t a_addr = smem0 + slot * STAGE_BYTES + r * A_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t row = (ct >> 2) + 32u * j, c = ct & 3u;
+              const uint32_t a_row = a_addr + row * 128u;
+              const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+              uint32_t ev[4], od[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                ev[i] = nibble_bytes_to_e4m3(w[i] & 0x0f0f0f0fu);
+                od[i] = nibble_bytes_to_e4m3((w[i] >> 4) & 0x0f0f0f0fu);
+              }
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c) ^ (row & 7u)) << 4)),
+                           "r"(ev[0]), "r"(ev[1]), "r"(ev[2]), "r"(ev[3])
+                           : "memory");
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c + 1u) ^ (row & 7u)) << 4)),
+                           "r"(od[0]), "r"(od[1]), "r"(od[2]), "r"(od[3])
+                           : "memory");
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(a_full(slot));
+            mbar_arrive(raw_empty(rslot));
+          }
+          if (++slot == NS) {
+            slot = 0;
+            ++round;
+          }
+          if (++rslot == RS) {
+            rslot = 0;
+            ++rround;
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take the group after next
       }
-      if (ok && active) {
+    }
+  } else if (warp >= kEpiWarp0) {
+    // ---- epilogue: warp e covers TMEM lanes 32*(warp % 4) .. +31 and half of the token columns ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // token scales, group sums, the output
+    const uint32_t e = warp - kEpiWarp0;
+    const uint32_t quarter = warp & 3u, half = e >> 2;
+    constexpr int CH = TT < 32 ? TT : 32;              // columns per tcgen05.ld when storing
+    constexpr int COLS = TT / 2 < CH ? CH : TT / 2;     // token columns of this warp
+    const uint32_t col0 = half * COLS;
+    const bool active = col0 < (uint32_t)TT;  // narrow tiles: the second half has nothing to do
+    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
+    const uint32_t row_in_tile = quarter * 32 + lane;
+    const float mult = ENC == AQ4 ? 512.0f : 1.0f;  // 2^9: the nibble bytes were read as u * 2^-9
+    constexpr uint64_t PART = (uint64_t)RT * TT * BM;  // floats of one partial tile
+    uint32_t seg = 0, group = 0;
+    bool ok = true;
+    while (walk.next(&sg)) {
+      uint32_t n0, m0;
+      tile_origin(sg.tile, &n0, &m0);
+      const bool direct = sg.contributors == 1;
+      float *part = direct ? nullptr : p.partial + ((uint64_t)blockIdx.x * 2 + (sg.head ? 0 : 1)) * PART;
+      // finished columns c .. c+CH-1 of row block r: final store, or this range's partial
+      auto emit = [&](int r, uint32_t c, const float (&v)[CH], bool final_pass) {
+        if (!final_pass) {
 #pragma unroll
-        for (int c = 0; c < COLS; c += 32) {
-          float f[32];
+          for (int i = 0; i < CH; ++i) part[((uint64_t)r * TT + c + i) * BM + row_in_tile] = v[i];
+          return;
+        }
+        const uint32_t row = n0 + r * BM + row_in_tile;
+        if (row >= p.n) return;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = acc[c + i];
-          store_chunk(col0 + c, f);
+        for (int i = 0; i < CH; ++i) {
+          const uint32_t tok = m0 + c + i;
+          if (tok < p.m) {
+            const float f = v[i] * (mult * __ldg(p.tok_scale + tok));
+            if (p.y_dtype == ULLM_CUDA_DTYPE_F32)
+              static_cast<float *>(p.y)[(uint64_t)tok * p.y_stride + row] = f;
+            else
+              static_cast<__nv_bfloat16 *>(p.y)[(uint64_t)tok * p.y_stride + row] = __float2bfloat16_rn(f);
+          }
+        }
+      };
+      if (ENC == FP8) {
+        const uint32_t buf = seg % NB, use = seg / NB;
+        ok = ok && mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+        if (ok) {
+          tc_fence_after();
+          if (active) {
+#pragma unroll 1
+            for (int r = 0; r < RT; ++r) {
+              const uint32_t row = n0 + r * BM + row_in_tile;
+              const float sc = row < p.n ? static_cast<const float *>(p.scales)[row] : 0.0f;
+#pragma unroll 1
+              for (int c = 0; c < COLS; c += CH) {
+                uint32_t v[CH];
+                tmem_ld(lane_addr + buf * ACC_COLS + r * TT + col0 + c, v);
+                tmem_ld_wait();
+                float f[CH];
+#pragma unroll
+                for (int i = 0; i < CH; ++i) f[i] = __uint_as_float(v[i]) * sc;
+                emit(r, col0 + c, f, direct);
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(buf));  // the accumulator may take the segment after next
+        }
+      } else {
+        static_assert(ENC != AQ4 || RT == 1, "the AQ4 epilogue keeps one row block's running sums in registers");
+        float acc[COLS];
+#pragma unroll
+        for (int i = 0; i < COLS; ++i) acc[i] = 0.0f;
+        const uint32_t groups = p.k / 128;
+        const uint32_t row = n0 + row_in_tile;
+        const __half *srow = static_cast<const __half *>(p.scales) + (uint64_t)(row < p.n ? row : 0) * groups + sg.kb0;
+        float sc_next = row < p.n ? __half2float(srow[0]) : 0.0f;
+        for (uint32_t g = 0; g < sg.nkb && ok; ++g, ++group) {
+          const uint32_t buf = group % NB, use = group / NB;
+          const float sc = sc_next;
+          if (g + 1 < sg.nkb && row < p.n) sc_next = __half2float(srow[g + 1]);
+          ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+          if (!ok) break;
+          tc_fence_after();
+          if (active) {
+#pragma unroll
+            for (int c = 0; c < COLS; c += CH) {
+              uint32_t v[CH];
+              tmem_ld(lane_addr + buf * ACC_COLS + col0 + c, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < CH; ++i) acc[c + i] = fmaf(sc, __uint_as_float(v[i]), acc[c + i]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take a later group
+        }
+        if (ok && active) {
+#pragma unroll
+          for (int c = 0; c < COLS; c += CH) {
+            float f[CH];
+#pragma unroll
+            for (int i = 0; i < CH; ++i) f[i] = acc[c + i];
+            emit(0, col0 + c, f, direct);
+          }
         }
       }
+      if (!direct) {
+        // the partial is in global memory; whoever arrives last at the tile's counter adds the partials in
+        // range order and stores.  All eight warps pass both barriers, also after a failed wait.
+        __threadfence();
+        epi_bar();
+        if (threadIdx.x == kEpiWarp0 * 32) {
+          uint32_t last = 0u;
+          if (ok) {
+            const uint32_t prev = atomicAdd(p.tile_counters + (sg.tile - p.sk_tile0), 1u);
+            if (prev + 1 == sg.contributors) {
+              p.tile_counters[sg.tile - p.sk_tile0] = 0u;  // ready for the next launch
+              last = 1u;
+            }
+          }
+          last_flag = last;
+        }
+        epi_bar();
+        if (last_flag != 0u && active) {
+          __threadfence();
+#pragma unroll 1
+          for (int r = 0; r < RT; ++r) {
+#pragma unroll 1
+            for (int c = 0; c < COLS; c += CH) {
+              float f[CH];
+#pragma unroll
+              for (int i = 0; i < CH; ++i) f[i] = 0.0f;
+              for (uint32_t j = 0; j < sg.contributors; ++j) {
+                // contributor j is range first_owner + j: its tail segment if it began the tile, else its head
+                const float *src = p.partial + ((uint64_t)(sg.first_owner + j) * 2 + (j == 0 ? 1 : 0)) * PART +
+                                   ((uint64_t)r * TT + col0 + c) * BM + row_in_tile;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) f[i] += __ldcg(src + (uint64_t)i * BM);
+              }
+              emit(r, col0 + c, f, true);
+            }
+          }
+        }
+        epi_bar();  // last_flag is rewritten by the next partial segment
+      }
+      ++seg;
     }
   }
-done:
   tc_fence_before();
   __syncthreads();
   if (abort_flag != 0u) {
@@ -440,43 +670,97 @@ done:
   }
 }
 
-// ---- elementwise helpers around the GEMM ------------------------------------------------------
+// ---- activations -> two e4m3 planes ------------------------------------------------------------
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// out[m][k] = bf16( prologue(x)[m][k] ), one block per row
-__global__ void prologue_kernel(const void *x, uint32_t x_dtype, uint64_t x_stride, uint32_t k, uint32_t prologue,
-                                float eps, __nv_bfloat16 *out) {
-  __shared__ float red[32];
-  const uint32_t m = blockIdx.x;
+// One block per token row m.  value[i] = bf16( prologue(x)[m][i] ) exactly as the matvec path stages it;
+// then planes[0][m][pos(i)] = hi, planes[1][m][pos(i)] = lo with value * 2^p = hi + lo, tok_scale[m] = 2^-p.
+// PERM (AQ4): inside every 32 consecutive k the even elements come first, then the odd ones, which is
+// the order the nibble conversion produces.
+template <bool PERM>
+__global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t x_dtype, uint64_t x_stride, uint32_t k,
+                                                         uint32_t prologue, float eps, uint8_t *planes,
+                                                         uint64_t plane_stride, float *tok_scale) {
+  __shared__ float red_ss[8], red_mx[8];
+  // the GEMM launched behind this kernel may set itself up now; it waits for this grid before reading
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t groups = k / 128;
   auto ld = [&](uint32_t i) -> float {
     return x_dtype == ULLM_CUDA_DTYPE_F32 ? bf16r(static_cast<const float *>(x)[(uint64_t)m * x_stride + i])
                                           : __bfloat162float(static_cast<const __nv_bfloat16 *>(x)[(uint64_t)m * x_stride + i]);
   };
-  float inv = 1.0f;
-  if (prologue == ULLM_CUDA_PROLOGUE_RMSNORM) {
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
-      const float v = ld(i);
-      ss = fmaf(v, v, ss);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float t = 0.0f;
-    for (uint32_t w = 0; w < blockDim.x / 32; ++w) t += red[w];
-    inv = 1.0f / sqrtf(t / (float)k + eps);
-  }
-  for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+  auto pre = [&](uint32_t i) -> float {
     float v = ld(i);
     if (prologue == ULLM_CUDA_PROLOGUE_SWIGLU) {
       const float u = ld(k + i);
       v = v / (1.0f + expf(-v)) * u;
-    } else if (prologue == ULLM_CUDA_PROLOGUE_RMSNORM) {
-      v = v * inv;
     }
-    out[(uint64_t)m * k + i] = __float2bfloat16_rn(v);
+    return v;
+  };
+  // pass 1: sum of squares (RMSNorm) and the largest magnitude
+  float ss = 0.0f, mx = 0.0f;
+  for (uint32_t g = warp; g < groups; g += 8) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float v = pre(g * 128 + lane * 4 + j);
+      ss = fmaf(v, v, ss);
+      mx = fmaxf(mx, fabsf(v));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) {
+    red_ss[warp] = ss;
+    red_mx[warp] = mx;
+  }
+  __syncthreads();
+  float tot = 0.0f, amax = 0.0f;
+  for (int w = 0; w < 8; ++w) {
+    tot += red_ss[w];
+    amax = fmaxf(amax, red_mx[w]);
+  }
+  const float inv = prologue == ULLM_CUDA_PROLOGUE_RMSNORM ? 1.0f / sqrtf(tot / (float)k + eps) : 1.0f;
+  amax = bf16r(amax * inv);  // rounding and the positive factor are monotone: this is the largest staged magnitude
+  int p = 0;
+  if (amax > 0.0f && amax <= 3.0e38f) {
+    int e;
+    (void)frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
+    p = 8 - e;               // amax * 2^p in [128, 256)
+    p = p > 126 ? 126 : (p < -126 ? -126 : p);
+  }
+  const float up = ldexpf(1.0f, p);
+  if (threadIdx.x == 0) tok_scale[m] = ldexpf(1.0f, -p);
+  // pass 2
+  uint8_t *hi_row = planes + (uint64_t)m * k, *lo_row = hi_row + plane_stride;
+  for (uint32_t g = warp; g < groups; g += 8) {
+    float xs[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xs[j] = bf16r(pre(g * 128 + lane * 4 + j) * inv) * up;
+    const uint32_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(xs[0], xs[1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(xs[2], xs[3]), __NV_SATFINITE, __NV_E4M3);
+    const float2 hf01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)h01, __NV_E4M3)));
+    const float2 hf23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)h23, __NV_E4M3)));
+    const uint32_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(xs[0] - hf01.x, xs[1] - hf01.y), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(xs[2] - hf23.x, xs[3] - hf23.y), __NV_SATFINITE, __NV_E4M3);
+    if (PERM) {
+      // elements 4j..4j+3 of a 32-chunk (j = lane % 8): 4j and 4j+2 are even elements 2j, 2j+1 -> positions 2j, 2j+1;
+      // 4j+1 and 4j+3 are odd elements 2j, 2j+1 -> positions 16+2j, 16+2j+1
+      const uint32_t base = g * 128 + (lane >> 3) * 32 + (lane & 7u) * 2;
+      const uint16_t h_even = (uint16_t)((h01 & 0xffu) | ((h23 & 0xffu) << 8)), h_odd = (uint16_t)((h01 >> 8) | (h23 & 0xff00u));
+      const uint16_t l_even = (uint16_t)((l01 & 0xffu) | ((l23 & 0xffu) << 8)), l_odd = (uint16_t)((l01 >> 8) | (l23 & 0xff00u));
+      *reinterpret_cast<uint16_t *>(hi_row + base) = h_even;
+      *reinterpret_cast<uint16_t *>(hi_row + base + 16) = h_odd;
+      *reinterpret_cast<uint16_t *>(lo_row + base) = l_even;
+      *reinterpret_cast<uint16_t *>(lo_row + base + 16) = l_odd;
+    } else {
+      *reinterpret_cast<uint32_t *>(hi_row + g * 128 + lane * 4) = (h01 & 0xffffu) | (h23 << 16);
+      *reinterpret_cast<uint32_t *>(lo_row + g * 128 + lane * 4) = (l01 & 0xffffu) | (l23 << 16);
+    }
   }
 }
 
@@ -507,27 +791,48 @@ EncodeTiled encode_tiled() {
   return fn;
 }
 
-// bf16 activations [m][k] with a row pitch: box = 64 (k) x tt (rows), 128-byte swizzle, zero fill outside
-bool make_x_map(CUtensorMap *map, const void *x, uint32_t m, uint32_t k, uint64_t stride_elems, uint32_t tt) {
+// activation planes [2][m][k] bytes: box = 128 (k) x tt (tokens) x 1 (plane), 128-byte swizzle, zero fill outside
+bool make_x_map(CUtensorMap *map, const void *planes, uint32_t m, uint32_t k, uint32_t tt) {
   EncodeTiled enc = encode_tiled();
   if (enc == nullptr) return false;
-  const cuuint64_t dims[2] = {k, m};
-  const cuuint64_t strides[1] = {stride_elems * 2};
-  const cuuint32_t box[2] = {BK, tt};
-  const cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {k, m, 2};
+  const cuuint64_t strides[2] = {k, (cuuint64_t)m * k};
+  const cuuint32_t box[3] = {BKB, tt, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(planes), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <uint32_t ENC, int TT>
-cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &map, GemmParams p) {
-  constexpr size_t stage = (size_t)BM * BK * 2 + (size_t)TT * BK * 2;
-  size_t ns = (220u * 1024u - 1024u) / stage;
-  if (ns > 8) ns = 8;
+// stored weight bytes [n][row_bytes]: FP8 box 128 B x 128 rows with the 128-byte swizzle (the operand tile
+// itself); AQ4 box 64 B x 128 rows, unswizzled (read back by the converter warps)
+bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_t enc_id) {
+  EncodeTiled enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const uint32_t row_bytes = enc_id == AQ4 ? k / 2 : k;
+  const cuuint64_t dims[2] = {row_bytes, n};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {enc_id == AQ4 ? BKB / 2u : (uint32_t)BKB, BM};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, enc_id == AQ4 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <uint32_t ENC, int TT, int RT>
+cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, GemmParams p, uint32_t grid) {
+  constexpr size_t stage = (size_t)RT * A_BYTES + 2 * (size_t)TT * BKB;
+  constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
+  constexpr size_t budget = 222u * 1024u - 1024u;
+  const size_t raw_min = ENC == AQ4 ? 3 : 0;
+  size_t ns = (budget - raw_min * raw_stage) / stage;
+  if (ns > MAX_STAGES) ns = MAX_STAGES;
+  size_t rs = ENC == AQ4 ? (budget - ns * stage) / raw_stage : 0;
+  if (rs > MAX_RAW) rs = MAX_RAW;
   p.stages = (uint32_t)ns;
-  const size_t smem = ns * stage + 1024;
-  auto kern = gemm_kernel<ENC, TT>;
+  p.raw_stages = (uint32_t)rs;
+  const size_t smem = ns * stage + rs * raw_stage + 1024;
+  auto kern = gemm_kernel<ENC, TT, RT>;
   static std::mutex mu;
   static bool configured = false;
   {
@@ -538,16 +843,170 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &map, GemmParams 
       configured = true;
     }
   }
-  dim3 grid((p.n + BM - 1) / BM, (p.m + TT - 1) / TT);
-  kern<<<grid, kThreads, smem, stream>>>(map, p);
-  return cudaGetLastError();
+  // programmatic dependent launch: barrier setup and tensor-memory allocation overlap the kernel that
+  // writes the activation planes; the roles that read its output wait for it (griddepcontrol.wait)
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, wmap, xmap, p);
+}
+
+int env_int(const char *name) {
+  const char *s = std::getenv(name);
+  return s ? std::atoi(s) : 0;
 }
 
 int tile_tokens(uint32_t m, uint32_t enc) {
-  const int cap = enc == AQ4 ? 128 : 256;  // AQ4 keeps TT/2 accumulators per epilogue thread in registers
-  int tt = 32;
+  static const int forced = env_int("ULLM_CUDA_GEMM_TOKENS");
+  const int cap = enc == AQ4 ? 128 : 256;  // AQ4 keeps TT/2 running sums per epilogue thread in registers
+  if (forced >= 16 && forced <= cap && (forced & (forced - 1)) == 0) return forced;
+  int tt = 16;
   while (tt < cap && (uint32_t)tt < m) tt *= 2;
   return tt;
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Where everything lives in the scratch area, and how the problem is cut up.
+struct Plan {
+  int tt = 0, rt = 1;
+  uint32_t tiles = 0, grid = 0, whole_rounds = 0, sk_tile0 = 0, sk_ctas = 0;
+  bool m_fastest = false;
+  size_t off_planes = 0, off_tok = 0, off_pair = 0, off_partial = 0, bytes = 0;
+};
+
+Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
+  Plan pl;
+  const uint32_t sms = ctx != nullptr && ctx->sm_count > 0 ? (uint32_t)ctx->sm_count : 148u;
+  pl.tt = tile_tokens(a.m, a.encoding);
+  // 256 weight rows per tile (two row blocks sharing the activation tile) once there is enough work for
+  // every SM: fewer activation bytes per FLOP through the L2 -> shared memory path
+  static const int forced_rows = env_int("ULLM_CUDA_GEMM_ROWS");
+  const uint32_t tiles_m = (a.m + pl.tt - 1) / pl.tt;
+  if (a.encoding == FP8 && pl.tt == 256) {
+    // measured: with two 96 KB stages the 256-row tile waits on its loads more than it saves (0.93 vs
+    // 1.06 PFLOP/s at 2048 x 14336 x 4096), so it is opt-in
+    pl.rt = forced_rows == 256 ? 2 : 1;
+  }
+  const uint32_t tiles_n = (a.n + pl.rt * BM - 1) / (pl.rt * BM);
+  const uint32_t kb = a.k / BKB;
+  pl.tiles = tiles_n * tiles_m;
+  uint32_t grid = pl.tiles < sms ? pl.tiles : sms;
+  // Whole tiles only: ceil(tiles / grid) rounds.  Hybrid: the full rounds whole, the remaining tiles cut
+  // along K over the CTAs, which costs each CTA up to two partial tiles (written, fenced, read back).
+  // Costs in k-block times; a partial of 128 x 256 fp32 is worth about five of them.
+  static const int forced_whole = env_int("ULLM_CUDA_GEMM_WHOLE");
+  const uint32_t full = pl.tiles / sms, rem = pl.tiles % sms;
+  const double part = 5.0 * pl.rt * pl.tt / 256.0;
+  const double cost_whole = (double)((pl.tiles + sms - 1) / sms) * kb;
+  const double cost_hybrid = (double)full * kb + (rem ? (double)rem * kb / sms + 2.0 * part : 0.0);
+  const bool hybrid = allow_partials && rem != 0 && (uint64_t)rem * kb >= 8 && forced_whole != 1 &&
+                      (forced_whole == 2 || cost_hybrid < cost_whole);
+  if (hybrid) {
+    grid = sms;
+    pl.whole_rounds = full;
+    pl.sk_tile0 = full * sms;
+    uint64_t ctas = (uint64_t)rem * kb / 4;  // at least four k-blocks per range
+    pl.sk_ctas = (uint32_t)(ctas > sms ? sms : ctas);
+  } else {
+    pl.whole_rounds = (pl.tiles + grid - 1) / grid;
+    pl.sk_tile0 = pl.tiles;
+    pl.sk_ctas = 0;
+  }
+  pl.grid = grid;
+  pl.m_fastest = (uint64_t)2 * a.m * a.k <= (uint64_t)96 << 20;  // the activation planes stay in L2
+  size_t off = 0;
+  pl.off_planes = off;
+  off += align256((size_t)2 * a.m * a.k);
+  pl.off_tok = off;
+  off += align256((size_t)a.m * 4);
+  pl.off_pair = off;
+  if (a.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU) off += align256((size_t)a.m * a.n * 2);
+  pl.off_partial = off;
+  if (pl.sk_ctas != 0) off += align256((size_t)pl.sk_ctas * 2 * pl.rt * pl.tt * BM * 4);
+  pl.bytes = off;
+  return pl;
+}
+
+// the planes and token scales of at most this many bytes of bf16 activations fit the static array
+constexpr size_t kStaticExtra = ULLM_CUDA_STATIC_SCRATCH_BYTES / 32 + 1024;
+
+cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &a, const Plan &pl, uint8_t *scratch,
+                     int *launches) {
+  uint8_t *planes = scratch + pl.off_planes;
+  float *tok = reinterpret_cast<float *>(scratch + pl.off_tok);
+  if (a.encoding == AQ4)
+    act_planes_kernel<true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, planes,
+                                                     (uint64_t)a.m * a.k, tok);
+  else
+    act_planes_kernel<false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, planes,
+                                                      (uint64_t)a.m * a.k, tok);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  const bool pair = a.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
+  GemmParams p{};
+  p.scales = a.scales;
+  p.tok_scale = tok;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.whole_rounds = pl.whole_rounds;
+  p.sk_tile0 = pl.sk_tile0;
+  p.sk_ctas = pl.sk_ctas;
+  p.m_fastest = pl.m_fastest ? 1u : 0u;
+  p.partial = pl.sk_ctas == 0 ? nullptr : reinterpret_cast<float *>(scratch + pl.off_partial);
+  p.tile_counters = ctx->tile_counters;
+  p.flags = ctx->device_flags;
+  if (pair) {  // gate|up to scratch as bf16, combined afterwards
+    p.y = scratch + pl.off_pair;
+    p.y_stride = a.n;
+    p.y_dtype = ULLM_CUDA_DTYPE_BF16;
+  } else {
+    p.y = a.y;
+    p.y_stride = a.y_stride;
+    p.y_dtype = a.y_dtype;
+  }
+  CUtensorMap wmap, xmap;
+  if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding) || !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)pl.tt))
+    return cudaErrorInvalidValue;
+  if (a.encoding == AQ4) {
+    switch (pl.tt) {
+      case 16: e = launch_tile<AQ4, 16, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 32: e = launch_tile<AQ4, 32, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 64: e = launch_tile<AQ4, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
+      default: e = launch_tile<AQ4, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
+    }
+  } else {
+    switch (pl.tt) {
+      case 16: e = launch_tile<FP8, 16, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 32: e = launch_tile<FP8, 32, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 64: e = launch_tile<FP8, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 128: e = launch_tile<FP8, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
+      default:
+        e = pl.rt == 2 ? launch_tile<FP8, 256, 2>(stream, wmap, xmap, p, pl.grid)
+                       : launch_tile<FP8, 256, 1>(stream, wmap, xmap, p, pl.grid);
+        break;
+    }
+  }
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  if (pair) {
+    dim3 g2((a.n / 2 + 255) / 256 > 64 ? 64 : (a.n / 2 + 255) / 256, a.m);
+    swiglu_kernel<<<g2, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(scratch + pl.off_pair), a.n / 2,
+                                          static_cast<__nv_bfloat16 *>(a.y), a.y_stride);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    ++*launches;
+  }
+  return cudaSuccess;
 }
 
 }  // namespace
@@ -555,6 +1014,10 @@ int tile_tokens(uint32_t m, uint32_t enc) {
 bool gemm_supports(const Context *, const LinearArgs &a, const char **why) {
   if (a.k % 128 != 0) {
     *why = "the GEMM kernel needs K to be a multiple of 128";
+    return false;
+  }
+  if (reinterpret_cast<uintptr_t>(a.w) % 16 != 0) {
+    *why = "the GEMM kernel needs the weight values 16-byte aligned";
     return false;
   }
   if (encode_tiled() == nullptr) {
@@ -568,6 +1031,12 @@ bool gemm_supports(const Context *, const LinearArgs &a, const char **why) {
 static cudaError_t ensure_scratch(const Context *cctx, size_t bytes, void **out) {
   Context *ctx = const_cast<Context *>(cctx);
   std::lock_guard<std::mutex> g(ctx->mutex);
+  if (ctx->tile_counters == nullptr) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&ctx->tile_counters), kMaxCounterTiles * sizeof(uint32_t));
+    if (e != cudaSuccess) return e;
+    e = cudaMemset(ctx->tile_counters, 0, kMaxCounterTiles * sizeof(uint32_t));
+    if (e != cudaSuccess) return e;
+  }
   if (ctx->scratch_bytes < bytes) {
     if (ctx->scratch != nullptr) {
       cudaError_t e = cudaFree(ctx->scratch);
@@ -585,22 +1054,15 @@ static cudaError_t ensure_scratch(const Context *cctx, size_t bytes, void **out)
 
 cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes) {
   void *unused = nullptr;
-  return bytes == 0 ? cudaSuccess : ensure_scratch(ctx, bytes, &unused);
+  return ensure_scratch(ctx, bytes, &unused);
 }
 
-size_t gemm_scratch_bytes(const LinearArgs &a) {
-  size_t bytes = 0;
-  const bool needs_x = a.prologue != ULLM_CUDA_PROLOGUE_NONE || a.x_dtype != ULLM_CUDA_DTYPE_BF16 ||
-                       reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (a.x_stride * 2) % 16 != 0;
-  if (needs_x) bytes += ((size_t)a.m * a.k * 2 + 255) & ~size_t(255);
-  if (a.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU) bytes += (size_t)a.m * a.n * 2;
-  return bytes;
-}
+size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a) { return make_plan(ctx, a, true).bytes; }
 
 // ---- allocation-free variant ---------------------------------------------------------------------
 // Staging area of the allocation-free entry point.  `g_static_scratch` names a host-side shadow in
 // host code, never a device address: the address is looked up once per device below.
-static __device__ __align__(256) uint8_t g_static_scratch[ULLM_CUDA_STATIC_SCRATCH_BYTES];
+static __device__ __align__(256) uint8_t g_static_scratch[ULLM_CUDA_STATIC_SCRATCH_BYTES + kStaticExtra];
 
 static cudaError_t static_scratch_address(int device, uint8_t **out) {
   constexpr int kMaxDevices = 64;
@@ -622,123 +1084,25 @@ static cudaError_t static_scratch_address(int device, uint8_t **out) {
 int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
   *err = cudaSuccess;
   if (a.epilogue != ULLM_CUDA_EPILOGUE_NONE) return -2;
-  const bool needs_x = a.prologue != ULLM_CUDA_PROLOGUE_NONE || a.x_dtype != ULLM_CUDA_DTYPE_BF16 ||
-                       reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (a.x_stride * 2) % 16 != 0;
-  if (needs_x && (uint64_t)a.m * a.k * 2 > ULLM_CUDA_STATIC_SCRATCH_BYTES) return -2;
-  int launches = 0;
-  const void *x = a.x;
-  uint64_t x_stride = a.x_stride;
-  if (needs_x) {
-    uint8_t *scratch = nullptr;
-    *err = static_scratch_address(ctx->device, &scratch);
-    if (*err != cudaSuccess) return -1;
-    __nv_bfloat16 *xb = reinterpret_cast<__nv_bfloat16 *>(scratch);
-    prologue_kernel<<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, xb);
-    *err = cudaGetLastError();
-    if (*err != cudaSuccess) return -1;
-    ++launches;
-    x = xb;
-    x_stride = a.k;
-  }
-  GemmParams p{};
-  p.w = a.w;
-  p.scales = a.scales;
-  p.m = a.m;
-  p.n = a.n;
-  p.k = a.k;
-  p.flags = ctx->device_flags;
-  p.y = a.y;
-  p.y_stride = a.y_stride;
-  p.y_dtype = a.y_dtype;
-  const int tt = tile_tokens(a.m, a.encoding);
-  CUtensorMap map;
-  if (!make_x_map(&map, x, a.m, a.k, x_stride, (uint32_t)tt)) {
-    *err = cudaErrorInvalidValue;
-    return -1;
-  }
-  if (a.encoding == AQ4) {
-    *err = tt == 32 ? launch_tile<AQ4, 32>(stream, map, p) : tt == 64 ? launch_tile<AQ4, 64>(stream, map, p)
-                                                                      : launch_tile<AQ4, 128>(stream, map, p);
-  } else {
-    *err = tt == 32    ? launch_tile<FP8, 32>(stream, map, p)
-           : tt == 64  ? launch_tile<FP8, 64>(stream, map, p)
-           : tt == 128 ? launch_tile<FP8, 128>(stream, map, p)
-                       : launch_tile<FP8, 256>(stream, map, p);
-  }
+  if ((uint64_t)a.m * a.k * 2 > ULLM_CUDA_STATIC_SCRATCH_BYTES) return -2;
+  const Plan pl = make_plan(ctx, a, false);  // whole tiles per CTA: partial tiles would need an allocation
+  if (pl.bytes > sizeof(g_static_scratch)) return -2;
+  uint8_t *scratch = nullptr;
+  *err = static_scratch_address(ctx->device, &scratch);
   if (*err != cudaSuccess) return -1;
-  return launches + 1;
+  int launches = 0;
+  *err = run_plan(ctx, stream, a, pl, scratch, &launches);
+  return *err == cudaSuccess ? launches : -1;
 }
 
 int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
+  const Plan pl = make_plan(ctx, a, true);
+  void *s = nullptr;
+  *err = ensure_scratch(ctx, pl.bytes, &s);
+  if (*err != cudaSuccess) return -1;
   int launches = 0;
-  const bool needs_x = a.prologue != ULLM_CUDA_PROLOGUE_NONE || a.x_dtype != ULLM_CUDA_DTYPE_BF16 ||
-                       reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (a.x_stride * 2) % 16 != 0;
-  const bool pair = a.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
-  uint8_t *scratch = nullptr;
-  const size_t need = gemm_scratch_bytes(a);
-  if (need != 0) {
-    void *s = nullptr;
-    *err = ensure_scratch(ctx, need, &s);
-    if (*err != cudaSuccess) return -1;
-    scratch = static_cast<uint8_t *>(s);
-  }
-  const void *x = a.x;
-  uint64_t x_stride = a.x_stride;
-  size_t off = 0;
-  if (needs_x) {
-    __nv_bfloat16 *xb = reinterpret_cast<__nv_bfloat16 *>(scratch);
-    prologue_kernel<<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, xb);
-    *err = cudaGetLastError();
-    if (*err != cudaSuccess) return -1;
-    ++launches;
-    x = xb;
-    x_stride = a.k;
-    off = ((size_t)a.m * a.k * 2 + 255) & ~size_t(255);
-  }
-  GemmParams p{};
-  p.w = a.w;
-  p.scales = a.scales;
-  p.m = a.m;
-  p.n = a.n;
-  p.k = a.k;
-  p.flags = ctx->device_flags;
-  if (pair) {  // gate|up to scratch as bf16, combined afterwards
-    p.y = scratch + off;
-    p.y_stride = a.n;
-    p.y_dtype = ULLM_CUDA_DTYPE_BF16;
-  } else {
-    p.y = a.y;
-    p.y_stride = a.y_stride;
-    p.y_dtype = a.y_dtype;
-  }
-  const int tt = tile_tokens(a.m, a.encoding);
-  CUtensorMap map;
-  if (!make_x_map(&map, x, a.m, a.k, x_stride, (uint32_t)tt)) {
-    *err = cudaErrorInvalidValue;
-    return -1;
-  }
-  cudaError_t e;
-  if (a.encoding == AQ4) {
-    e = tt == 32 ? launch_tile<AQ4, 32>(stream, map, p) : tt == 64 ? launch_tile<AQ4, 64>(stream, map, p)
-                                                                   : launch_tile<AQ4, 128>(stream, map, p);
-  } else {
-    e = tt == 32    ? launch_tile<FP8, 32>(stream, map, p)
-        : tt == 64  ? launch_tile<FP8, 64>(stream, map, p)
-        : tt == 128 ? launch_tile<FP8, 128>(stream, map, p)
-                    : launch_tile<FP8, 256>(stream, map, p);
-  }
-  *err = e;
-  if (e != cudaSuccess) return -1;
-  ++launches;
-  if (pair) {
-    dim3 grid((a.n / 2 + 255) / 256 > 64 ? 64 : (a.n / 2 + 255) / 256, a.m);
-    swiglu_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(scratch + off), a.n / 2,
-                                           static_cast<__nv_bfloat16 *>(a.y), a.y_stride);
-    *err = cudaGetLastError();
-    if (*err != cudaSuccess) return -1;
-    ++launches;
-  }
-  return launches;
+  *err = run_plan(ctx, stream, a, pl, static_cast<uint8_t *>(s), &launches);
+  return *err == cudaSuccess ? launches : -1;
 }
 
 }  // namespace ullm

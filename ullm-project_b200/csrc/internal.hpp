@@ -92,6 +92,7 @@ struct Context {
   uint32_t *device_flags = nullptr;  // device view of host_flags: kernels set a word when a bounded wait expires
   void *scratch = nullptr;           // grow-only device scratch of the GEMM path (prologue output, gate|up)
   size_t scratch_bytes = 0;
+  uint32_t *tile_counters = nullptr;  // split-K arrival counters of the GEMM path, zero between launches
   std::mutex mutex;
   std::vector<cudaEvent_t> event_pool;
   std::atomic<uint64_t> live_children{0};
@@ -275,7 +276,7 @@ int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cu
 int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
 // Scratch bytes launch_gemm needs for these arguments, and a way to reserve them ahead of
 // time (the scratch may not grow while a stream is being captured).
-size_t gemm_scratch_bytes(const LinearArgs &a);
+size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a);
 cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes);
 bool gemm_supports(const Context *ctx, const LinearArgs &a, const char **why);
 

@@ -310,6 +310,7 @@ ullm_status_t ullm_cuda_context_destroy(ullm_cuda_context_t **context, ullm_cuda
   for (cudaEvent_t ev : c->event_pool) (void)cudaEventDestroy(ev);
   (void)cudaFreeHost(c->host_flags);
   if (c->scratch != nullptr) (void)cudaFree(c->scratch);
+  if (c->tile_counters != nullptr) (void)cudaFree(c->tile_counters);
   c->magic = 0;
   delete c;
   *context = nullptr;

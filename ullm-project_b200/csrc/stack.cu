@@ -529,9 +529,14 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   // ---- reserve the GEMM path's scratch for the largest step (it cannot grow during capture) ----
   if (d.max_tokens > 8) {
     size_t need = 0;
+    // the need is not monotone in the token count (narrow tiles split K more ways): try every tile width
     for (const StackLinear &L : S->linears) {
-      const size_t b = gemm_scratch_bytes(make_args(S, L, d.max_tokens));
-      need = b > need ? b : need;
+      for (uint32_t m = 16; ; m *= 2) {
+        const uint32_t tokens = m < d.max_tokens ? m : d.max_tokens;
+        const size_t b = gemm_scratch_bytes(ctx, make_args(S, L, tokens));
+        need = b > need ? b : need;
+        if (tokens == d.max_tokens) break;
+      }
     }
     e = gemm_reserve_scratch(ctx, need);
     if (e != cudaSuccess) {
