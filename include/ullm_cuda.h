@@ -266,7 +266,7 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_dequantize(ullm_cuda_queue_t *queue, const
 #define ULLM_CUDA_EPILOGUE_SWIGLU UINT32_C(1)
 
 #define ULLM_CUDA_KERNEL_AUTO UINT32_C(0)
-#define ULLM_CUDA_KERNEL_MATVEC UINT32_C(1) /* CUDA-core streaming kernel, M <= 8 */
+#define ULLM_CUDA_KERNEL_MATVEC UINT32_C(1) /* CUDA-core streaming kernel, M <= 8; AUTO picks it for M = 1 (AQ4: M <= 4) */
 #define ULLM_CUDA_KERNEL_GEMM UINT32_C(2)   /* tcgen05 / TMEM kernel */
 
 typedef struct ullm_cuda_linear_desc_t {

@@ -91,11 +91,20 @@ def test_gemm_swiglu_epilogue_and_strides(gpu, encoding):
     dw.close()
 
 
-def test_auto_selects_gemm_above_eight_tokens(gpu):
+def test_auto_selects_the_faster_kernel_for_the_token_count(gpu):
+    """AUTO: the matvec for one token (AQ4: up to four), the tensor-core GEMM above that where it serves the shape."""
     ctx, q = gpu
-    w = U.abi.Weight(U.ENCODING_FP8_CHANNEL, 0, 256, 512, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))
-    assert U.linear_supports(U.linear_desc(w, 8, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))) == U.KERNEL_MATVEC
-    assert U.linear_supports(U.linear_desc(w, 9, U.abi.Tensor(None, 0), U.abi.Tensor(None, 0))) == U.KERNEL_GEMM
+    none = U.abi.Tensor(None, 0)
+    fp8 = U.abi.Weight(U.ENCODING_FP8_CHANNEL, 0, 256, 512, none, none)
+    aq4 = U.abi.Weight(U.ENCODING_AQ4, 128, 256, 512, none, none)
+    assert U.linear_supports(U.linear_desc(fp8, 1, none, none)) == U.KERNEL_MATVEC
+    assert U.linear_supports(U.linear_desc(fp8, 2, none, none)) == U.KERNEL_GEMM
+    assert U.linear_supports(U.linear_desc(aq4, 4, none, none)) == U.KERNEL_MATVEC
+    assert U.linear_supports(U.linear_desc(aq4, 5, none, none)) == U.KERNEL_GEMM
+    assert U.linear_supports(U.linear_desc(fp8, 9, none, none)) == U.KERNEL_GEMM
+    # K = 80 is no multiple of 128: only the matvec serves it
+    odd = U.abi.Weight(U.ENCODING_FP8_CHANNEL, 0, 256, 80, none, none)
+    assert U.linear_supports(U.linear_desc(odd, 4, none, none)) == U.KERNEL_MATVEC
 
 
 def test_prefill_shape_on_sampled_rows(gpu):

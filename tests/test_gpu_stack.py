@@ -60,7 +60,8 @@ def test_tiny_stack_every_linear_matches_the_oracle(gpu, encoding, name, m, flag
     q.synchronize()
     assert np.array_equal(q.download(yout.at(0), (m, TINY.vocab), np.uint16), st.step_host(xb))
     wb, launches = st.stats()
-    assert launches == TINY.layers * 4 + 1
+    linears = TINY.layers * 4 + 1  # one matvec launch each, or activation planes + GEMM (+ SwiGLU) on the tensor-core path
+    assert linears <= launches <= 3 * linears
     per = {U.ENCODING_AQ4: lambda n, k: n * k // 2 + n * k // 64, U.ENCODING_FP8_CHANNEL: lambda n, k: n * k + 4 * n}[encoding]
     want = TINY.layers * (per(qd + 2 * TINY.kv_heads * TINY.head_dim, TINY.hidden) + per(TINY.hidden, qd)
                           + per(2 * TINY.ffn, TINY.hidden) + per(TINY.hidden, TINY.ffn)) + per(TINY.vocab, TINY.hidden)

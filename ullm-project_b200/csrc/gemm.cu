@@ -32,7 +32,7 @@
 //   warps 4-7   AQ4 only: nibble tile -> e4m3 operand tile (shared memory to shared memory)
 //   warps 8-15  epilogue: tcgen05.ld, scales, store (or split-K partial + last-arriver sum)
 // FP8: all k-blocks accumulate in one tensor-memory buffer.  AQ4: one buffer per 128-deep scale
-// group, two or four in rotation, drained into fp32 registers as scale[n,g] * partial.
+// group, handed to the epilogue in batches, drained into fp32 registers as scale[n,g] * partial.
 // Accumulators are double-buffered in tensor memory, so the epilogue of one tile overlaps the MMAs of
 // the next.  A tile whose k-blocks fall into several CTAs' shares is finished by the CTA that arrives
 // last at the tile's counter, adding the fp32 partials in a fixed order (deterministic).
@@ -45,6 +45,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace ullm {
@@ -60,6 +61,7 @@ constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
 constexpr uint32_t A_BYTES = BM * BKB;        // e4m3 operand tile
 constexpr uint32_t RAW_BYTES = BM * BKB / 2;  // packed nibble tile
 constexpr int MAX_STAGES = 8, MAX_RAW = 8;
+static_assert(MAX_STAGES % kConvWarps == 0 && MAX_RAW % kConvWarps == 0, "ring lengths are multiples of the converter warps");
 constexpr uint32_t kFlagGemmWait = 2u;
 constexpr uint64_t kWaitLimitNs = 20ull * 1000ull * 1000ull * 1000ull;
 constexpr uint32_t kMaxCounterTiles = 1024;  // phase-2 tiles: fewer than the SM count
@@ -79,6 +81,7 @@ struct GemmParams {
   float *partial;           // [range][head, tail][row block][TT][128] fp32
   uint32_t *tile_counters;  // one per phase-2 tile, zero between launches
   uint32_t *flags;
+  unsigned long long *trace;  // diagnostic: CTA 0 adds up the cycles its roles spend waiting (null: off)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -185,12 +188,14 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory"); }
 
-// K-major, 128-byte-swizzled operand tile (rows of 128 bytes, 8-row groups 1024 bytes apart):
-// start address >> 4, leading byte offset 1 (unused with a swizzle), stride byte offset 1024 >> 4,
-// descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+// K-major swizzled operand tile whose rows are KS = 128 or 64 bytes (the swizzle span) and whose 8-row groups
+// are 8 * KS bytes apart: start address >> 4, leading byte offset 1 (unused with a swizzle), stride byte offset
+// (8 * KS) >> 4, descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B) or 4 (SWIZZLE_64B).
+template <int KS>
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
+  static_assert(KS == 128 || KS == 64, "swizzle span");
   const uint32_t lo = ((smem_addr >> 4) & 0x3fffu) | (1u << 16);
-  const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+  const uint32_t hi = (uint32_t)(8 * KS / 16) | (1u << 14) | ((KS == 128 ? 2u : 4u) << 29);
   return ((uint64_t)hi << 32) | lo;
 }
 
@@ -264,6 +269,22 @@ struct Walker {
   }
 };
 
+// Diagnostic stopwatch: cycles between construction/lap() calls are added to trace[slot] by CTA 0's role leaders.
+struct Lap {
+  unsigned long long *trace;
+  long long t;
+  __device__ Lap(unsigned long long *tr, bool leader) : trace(leader && blockIdx.x == 0 ? tr : nullptr), t(0) {
+    if (trace) t = clock64();
+  }
+  __device__ void lap(int slot) {
+    if (trace) {
+      const long long now = clock64();
+      trace[slot] += (unsigned long long)(now - t);
+      t = now;
+    }
+  }
+};
+
 // Four bytes, each holding a nibble u = q + 8 (0..15): each becomes the e4m3 byte of q * 2^-9, that is
 // |q| with the sign in bit 7 (|q| <= 8 sits in the linear part of e4m3, where the byte value is the magnitude).
 __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
@@ -272,17 +293,33 @@ __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
   return r0 + m * 129u;                             // negative: + 1 -> 8 - u, and bit 7
 }
 
-template <uint32_t ENC, int TT, int RT>
+template <uint32_t ENC, int TT, int RT, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   extern __shared__ uint8_t smem_dyn[];
-  constexpr uint32_t B_BYTES = (uint32_t)TT * BKB;  // one activation plane of the stage
-  constexpr uint32_t STAGE_BYTES = RT * A_BYTES + 2 * B_BYTES;
-  constexpr uint32_t ACC_COLS = (uint32_t)(RT * TT);  // one accumulator set: RT row blocks side by side
-  // accumulator sets in tensor memory: AQ4 one per scale group in rotation, FP8 one per segment
-  constexpr int NB = ENC == AQ4 ? (ACC_COLS > 128 ? 2 : 4) : (ACC_COLS > 256 ? 1 : 2);
-  constexpr uint32_t TMEM_COLS = tmem_cols(ACC_COLS * NB);
-  static_assert(ACC_COLS * NB <= 512, "tensor memory has 512 columns");
+  // a stage holds KS bytes of k: a whole k-block, or half of one where the tiles are too large for more
+  // than two whole-k-block stages (the loads of a 96 KB stage take longer than its MMAs)
+  static_assert(KS == BKB || ENC == FP8, "the AQ4 converters write whole k-blocks");
+  constexpr uint32_t SUBS = BKB / KS;                   // stages per k-block
+  constexpr uint32_t A_STAGE = (uint32_t)BM * KS;       // one row block of the stage
+  constexpr uint32_t B_BYTES = (uint32_t)TT * KS;       // one activation plane of the stage
+  constexpr uint32_t STAGE_BYTES = RT * A_STAGE + 2 * B_BYTES;
+  // Up to 64 tokens the two activation planes, adjacent in shared memory, are ONE operand of 2*TT rows: a
+  // single MMA per k-slice leaves A.hi in columns [0,TT) and A.lo in [TT,2TT) and the epilogue adds them.
+  // A narrow MMA costs the tensor pipe about as much as a wide one, so this halves the pipe time where
+  // the weight stream should set the pace.
+  constexpr bool NCAT = TT <= 64;
+  constexpr uint32_t MMA_N = NCAT ? 2u * TT : (uint32_t)TT;
+  constexpr uint32_t ACC_COLS = RT * MMA_N;  // one accumulator set: RT row blocks side by side
+  // Accumulator sets in tensor memory.  FP8: one per segment, two in rotation when they fit.  AQ4: one per
+  // 128-deep scale group; GB consecutive groups form a batch that is handed to the epilogue with one
+  // barrier round trip, two batches in rotation.
+  // (Wide tiles keep one group per batch and four in rotation: measured 0.63 vs 0.57 PFLOP/s at 2048 tokens.)
+  constexpr uint32_t GB = (ENC == AQ4 && ACC_COLS < 128) ? 256u / ACC_COLS : 1u;  // groups per batch
+  constexpr int NB = ENC == AQ4 ? (GB > 1 ? 2 : 4) : (ACC_COLS > 256 ? 1 : 2);
+  constexpr uint32_t BUF_COLS = GB * ACC_COLS;
+  constexpr uint32_t TMEM_COLS = tmem_cols(BUF_COLS * NB);
+  static_assert(BUF_COLS * NB <= 512, "tensor memory has 512 columns");
   __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 2 * MAX_RAW + 8];
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_flag;
@@ -314,12 +351,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     last_flag = 0u;
     for (uint32_t s = 0; s < NS; ++s) {
       mbar_init(full(s), 1u);                       // the TMA thread's expect_tx
-      mbar_init(a_full(s), (uint32_t)kConvWarps);   // one arrival per converter warp
+      mbar_init(a_full(s), 1u);                     // the converter warp that owns the k-block
       mbar_init(empty(s), 1u);                      // tcgen05.commit
     }
     for (uint32_t s = 0; s < RS; ++s) {
       mbar_init(raw_full(s), 1u);
-      mbar_init(raw_empty(s), (uint32_t)kConvWarps);
+      mbar_init(raw_empty(s), 1u);
     }
     for (uint32_t b = 0; b < 4; ++b) {
       mbar_init(acc_full(b), 1u);                     // tcgen05.commit
@@ -346,23 +383,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t slot = 0, round = 0;
       bool ok = true;
+      Lap lap(p.trace, true);
       while (ok && walk.next(&sg)) {
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
-        for (uint32_t i = 0; i < sg.nkb; ++i) {
+        for (uint32_t i = 0; i < sg.nkb * SUBS; ++i) {
+          lap.lap(0);
           if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
             ok = false;
             break;
           }
+          lap.lap(1);
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES;
-          const int kx = (int)((sg.kb0 + i) * BKB);
-          mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_BYTES : 0u) + 2 * B_BYTES);
+          const int kx = (int)(sg.kb0 * BKB + i * KS);
+          mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_STAGE : 0u) + 2 * B_BYTES);
           if (ENC == FP8) {
 #pragma unroll
-            for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_BYTES, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
+            for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_STAGE, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
           }
-          tma_load_3d(a_addr + RT * A_BYTES, &tmap_x, kx, (int)m0, 0, full(slot));
-          tma_load_3d(a_addr + RT * A_BYTES + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
+          tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
+          tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
           if (++slot == NS) {
             slot = 0;
             ++round;
@@ -373,45 +413,56 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ---- MMA issue ------------------------------------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_e4m3(TT);
-      uint32_t slot = 0, round = 0, seg = 0, group = 0;
+      constexpr uint32_t idesc = instr_desc_e4m3((int)MMA_N);
+      uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
+      Lap lap(p.trace, true);
       while (ok && walk.next(&sg)) {
         uint32_t buf = 0;
         if (ENC == FP8) {
           buf = seg % NB;
           const uint32_t use = seg / NB;
+          lap.lap(2);
           if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+          lap.lap(3);
         }
-        for (uint32_t i = 0; i < sg.nkb && ok; ++i) {
+        for (uint32_t i = 0; i < sg.nkb * SUBS && ok; ++i) {
           uint32_t fresh = i == 0 ? 1u : 0u;
           if (ENC == AQ4) {
-            buf = group % NB;
-            const uint32_t use = group / NB;
+            buf = batch % NB;
+            const uint32_t use = batch / NB;
             fresh = 1u;
-            if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+            lap.lap(2);
+            if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+            lap.lap(3);
             ok = ok && mbar_wait(a_full(slot), round & 1u, &abort_flag, p.flags);
+            lap.lap(4);
           }
+          lap.lap(2);
           ok = ok && mbar_wait(full(slot), round & 1u, &abort_flag, p.flags);
+          lap.lap(5);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_BYTES, lo_addr = hi_addr + B_BYTES;
+          const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
-            const uint32_t d = tmem_base + buf * ACC_COLS + r * TT;
+            const uint32_t d = tmem_base + buf * BUF_COLS + in_batch * ACC_COLS + r * MMA_N;
 #pragma unroll
-            for (int k4 = 0; k4 < BKB / 32; ++k4) {
+            for (int k4 = 0; k4 < KS / 32; ++k4) {
               // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
-              const uint64_t adesc = smem_desc_sw128(a_addr + r * A_BYTES + k4 * 32);
-              tc_mma_e4m3(d, adesc, smem_desc_sw128(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-              tc_mma_e4m3(d, adesc, smem_desc_sw128(lo_addr + k4 * 32), idesc, 1u);
+              const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
+              tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
+              if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc, 1u);
             }
           }
           tc_commit(empty(slot));  // the stage may be refilled when these MMAs are done
           if (ENC == AQ4) {
-            tc_commit(acc_full(buf));
-            ++group;
-          } else if (i + 1 == sg.nkb) {
+            if (++in_batch == GB || i + 1 == sg.nkb) {  // a batch does not span tiles
+              tc_commit(acc_full(buf));
+              ++batch;
+              in_batch = 0;
+            }
+          } else if (i + 1 == sg.nkb * SUBS) {
             tc_commit(acc_full(buf));
           }
           if (++slot == NS) {
@@ -449,47 +500,65 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp >= kConvWarp0 && warp < kConvWarp0 + kConvWarps) {
     // ---- AQ4: nibble tile -> e4m3 operand tile ------------------------------------------------
-    // Item (row, c): the 16 bytes c of the row's 64 = k 32c .. 32c+31.  The even elements of those 32 go
-    // to operand chunk 2c, the odd ones to chunk 2c+1; the activation planes use the same order.
+    // Converter warp w owns the k-blocks whose running number is w modulo the number of converter warps and
+    // converts all 128 rows of them, so a warp's shared-memory latencies and its proxy fence overlap the
+    // other warps' work on the neighbouring k-blocks.  Both rings are multiples of that number long, so a
+    // warp always meets the same slots and waits on each of their phases in turn (a parity wait that skipped
+    // a phase would pass on the wrong one).
     if (ENC == AQ4) {
-      const uint32_t ct = threadIdx.x - kConvWarp0 * 32;
-      uint32_t slot = 0, round = 0, rslot = 0, rround = 0;
+      const uint32_t cw = warp - kConvWarp0;
+      uint32_t number = 0;  // running k-block number over all segments
       bool ok = true;
+      Lap lap(p.trace, cw == 0 && lane == 0);
       while (ok && walk.next(&sg)) {
-        for (uint32_t i = 0; i < sg.nkb; ++i) {
-          if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags) ||
-              (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags))) {
+        for (uint32_t i = 0; i < sg.nkb; ++i, ++number) {
+          if (number % kConvWarps != cw) continue;
+          const uint32_t slot = number % NS, round = number / NS, rslot = number % RS, rround = number / RS;
+          lap.lap(6);
+          if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags)) {
             ok = false;
             break;
           }
+          lap.lap(7);
+          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+            ok = false;
+            break;
+          }
+          lap.lap(8);
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
-            uint4 q[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t addr = raw0 + (rslot * RT + r) * RAW_BYTES + (ct + 128u * j) * 16u;
-              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
-                           : "r"(addr));
-            }
+            const uint32_t raw_addr = raw0 + (rslot * RT + r) * RAW_BYTES;
             const uint32_t a_addr = smem0 + slot * STAGE_BYTES + r * A_BYTES;
+#pragma unroll 1
+            for (int jb = 0; jb < 16; jb += 4) {
+              uint4 q[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t row = (ct >> 2) + 32u * j, c = ct & 3u;
-              const uint32_t a_row = a_addr + row * 128u;
-              const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-              uint32_t ev[4], od[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                ev[i] = nibble_bytes_to_e4m3(w[i] & 0x0f0f0f0fu);
-                od[i] = nibble_bytes_to_e4m3((w[i] >> 4) & 0x0f0f0f0fu);
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t addr = raw_addr + (lane + 32u * (jb + j)) * 16u;
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
+                             : "r"(addr));
               }
-              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c) ^ (row & 7u)) << 4)),
-                           "r"(ev[0]), "r"(ev[1]), "r"(ev[2]), "r"(ev[3])
-                           : "memory");
-              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c + 1u) ^ (row & 7u)) << 4)),
-                           "r"(od[0]), "r"(od[1]), "r"(od[2]), "r"(od[3])
-                           : "memory");
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                // item (row, c): the 16 bytes c of the row's 64 = k 32c .. 32c+31; the even elements of those 32
+                // go to operand chunk 2c, the odd ones to chunk 2c+1 (the activation planes use the same order)
+                const uint32_t row = (lane >> 2) + 8u * (jb + j), c = lane & 3u;
+                const uint32_t a_row = a_addr + row * 128u;
+                const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+                uint32_t ev[4], od[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  ev[t] = nibble_bytes_to_e4m3(w[t] & 0x0f0f0f0fu);
+                  od[t] = nibble_bytes_to_e4m3((w[t] >> 4) & 0x0f0f0f0fu);
+                }
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c) ^ (row & 7u)) << 4)),
+                             "r"(ev[0]), "r"(ev[1]), "r"(ev[2]), "r"(ev[3])
+                             : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c + 1u) ^ (row & 7u)) << 4)),
+                             "r"(od[0]), "r"(od[1]), "r"(od[2]), "r"(od[3])
+                             : "memory");
+              }
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
@@ -497,14 +566,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) {
             mbar_arrive(a_full(slot));
             mbar_arrive(raw_empty(rslot));
-          }
-          if (++slot == NS) {
-            slot = 0;
-            ++round;
-          }
-          if (++rslot == RS) {
-            rslot = 0;
-            ++rround;
           }
         }
       }
@@ -522,8 +583,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t row_in_tile = quarter * 32 + lane;
     const float mult = ENC == AQ4 ? 512.0f : 1.0f;  // 2^9: the nibble bytes were read as u * 2^-9
     constexpr uint64_t PART = (uint64_t)RT * TT * BM;  // floats of one partial tile
-    uint32_t seg = 0, group = 0;
+    uint32_t seg = 0, batch = 0;
     bool ok = true;
+    Lap lap(p.trace, e == 0 && lane == 0);
     while (walk.next(&sg)) {
       uint32_t n0, m0;
       tile_origin(sg.tile, &n0, &m0);
@@ -552,7 +614,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       if (ENC == FP8) {
         const uint32_t buf = seg % NB, use = seg / NB;
+        lap.lap(9);
         ok = ok && mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+        lap.lap(10);
         if (ok) {
           tc_fence_after();
           if (active) {
@@ -562,12 +626,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               const float sc = row < p.n ? static_cast<const float *>(p.scales)[row] : 0.0f;
 #pragma unroll 1
               for (int c = 0; c < COLS; c += CH) {
-                uint32_t v[CH];
-                tmem_ld(lane_addr + buf * ACC_COLS + r * TT + col0 + c, v);
+                uint32_t v[CH], v2[CH];
+                tmem_ld(lane_addr + buf * BUF_COLS + r * MMA_N + col0 + c, v);
+                if (NCAT) tmem_ld(lane_addr + buf * BUF_COLS + r * MMA_N + TT + col0 + c, v2);
                 tmem_ld_wait();
                 float f[CH];
 #pragma unroll
-                for (int i = 0; i < CH; ++i) f[i] = __uint_as_float(v[i]) * sc;
+                for (int i = 0; i < CH; ++i)
+                  f[i] = (NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i])) * sc;
                 emit(r, col0 + c, f, direct);
               }
             }
@@ -584,27 +650,39 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t groups = p.k / 128;
         const uint32_t row = n0 + row_in_tile;
         const __half *srow = static_cast<const __half *>(p.scales) + (uint64_t)(row < p.n ? row : 0) * groups + sg.kb0;
-        float sc_next = row < p.n ? __half2float(srow[0]) : 0.0f;
-        for (uint32_t g = 0; g < sg.nkb && ok; ++g, ++group) {
-          const uint32_t buf = group % NB, use = group / NB;
-          const float sc = sc_next;
-          if (g + 1 < sg.nkb && row < p.n) sc_next = __half2float(srow[g + 1]);
+        for (uint32_t g = 0; g < sg.nkb && ok; ++batch) {
+          const uint32_t cnt = sg.nkb - g < GB ? sg.nkb - g : GB;  // groups in this batch
+          const uint32_t buf = batch % NB, use = batch / NB;
+          float sc[GB];
+#pragma unroll
+          for (uint32_t j = 0; j < GB; ++j) sc[j] = (j < cnt && row < p.n) ? __half2float(srow[g + j]) : 0.0f;
+          lap.lap(9);
           ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+          lap.lap(10);
           if (!ok) break;
           tc_fence_after();
           if (active) {
 #pragma unroll
-            for (int c = 0; c < COLS; c += CH) {
-              uint32_t v[CH];
-              tmem_ld(lane_addr + buf * ACC_COLS + col0 + c, v);
-              tmem_ld_wait();
+            for (uint32_t j = 0; j < GB; ++j) {
+              if (j < cnt) {
 #pragma unroll
-              for (int i = 0; i < CH; ++i) acc[c + i] = fmaf(sc, __uint_as_float(v[i]), acc[c + i]);
+                for (int c = 0; c < COLS; c += CH) {
+                  uint32_t v[CH], v2[CH];
+                  tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + col0 + c, v);
+                  if (NCAT) tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + TT + col0 + c, v2);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int i = 0; i < CH; ++i)
+                    acc[c + i] =
+                        fmaf(sc[j], NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]), acc[c + i]);
+                }
+              }
             }
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take a later group
+          if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take the batch after next
+          g += cnt;
         }
         if (ok && active) {
 #pragma unroll
@@ -657,6 +735,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ++seg;
     }
+    lap.lap(9);
   }
   tc_fence_before();
   __syncthreads();
@@ -792,47 +871,60 @@ EncodeTiled encode_tiled() {
 }
 
 // activation planes [2][m][k] bytes: box = 128 (k) x tt (tokens) x 1 (plane), 128-byte swizzle, zero fill outside
-bool make_x_map(CUtensorMap *map, const void *planes, uint32_t m, uint32_t k, uint32_t tt) {
+bool make_x_map(CUtensorMap *map, const void *planes, uint32_t m, uint32_t k, uint32_t tt, uint32_t ks) {
   EncodeTiled enc = encode_tiled();
   if (enc == nullptr) return false;
   const cuuint64_t dims[3] = {k, m, 2};
   const cuuint64_t strides[2] = {k, (cuuint64_t)m * k};
-  const cuuint32_t box[3] = {BKB, tt, 1};
+  const cuuint32_t box[3] = {ks, tt, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(planes), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+             CU_TENSOR_MAP_INTERLEAVE_NONE, ks == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // stored weight bytes [n][row_bytes]: FP8 box 128 B x 128 rows with the 128-byte swizzle (the operand tile
 // itself); AQ4 box 64 B x 128 rows, unswizzled (read back by the converter warps)
-bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_t enc_id) {
+bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_t enc_id, uint32_t ks) {
   EncodeTiled enc = encode_tiled();
   if (enc == nullptr) return false;
   const uint32_t row_bytes = enc_id == AQ4 ? k / 2 : k;
   const cuuint64_t dims[2] = {row_bytes, n};
   const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {enc_id == AQ4 ? BKB / 2u : (uint32_t)BKB, BM};
+  const cuuint32_t box[2] = {enc_id == AQ4 ? BKB / 2u : ks, BM};
   const cuuint32_t estr[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, enc_id == AQ4 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE,
+             enc_id == AQ4 ? CU_TENSOR_MAP_SWIZZLE_NONE : (ks == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <uint32_t ENC, int TT, int RT>
+template <uint32_t ENC, int TT, int RT, int KS = BKB>
 cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, GemmParams p, uint32_t grid) {
-  constexpr size_t stage = (size_t)RT * A_BYTES + 2 * (size_t)TT * BKB;
+  constexpr size_t stage = (size_t)RT * BM * KS + 2 * (size_t)TT * KS;
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
-  constexpr size_t budget = 222u * 1024u - 1024u;
-  const size_t raw_min = ENC == AQ4 ? 3 : 0;
-  size_t ns = (budget - raw_min * raw_stage) / stage;
-  if (ns > MAX_STAGES) ns = MAX_STAGES;
-  size_t rs = ENC == AQ4 ? (budget - ns * stage) / raw_stage : 0;
-  if (rs > MAX_RAW) rs = MAX_RAW;
+  constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
+  size_t ns = 0, rs = 0;
+  if (ENC == AQ4) {
+    // A converter warp must see every phase of the barriers it waits on, so it keeps the same slots for the
+    // whole kernel: both ring lengths are multiples of the number of converter warps.
+    const size_t room = budget;
+    if (8 * stage + 4 * raw_stage <= room) {
+      ns = 8;
+      rs = 8 * stage + 8 * raw_stage <= room ? 8 : 4;
+    } else {
+      ns = 4;
+      rs = 4 * stage + 8 * raw_stage <= room ? 8 : 4;
+    }
+    if (ns * stage + rs * raw_stage > room) return cudaErrorInvalidConfiguration;
+  } else {
+    ns = budget / stage;
+    if (ns > MAX_STAGES) ns = MAX_STAGES;
+  }
   p.stages = (uint32_t)ns;
   p.raw_stages = (uint32_t)rs;
   const size_t smem = ns * stage + rs * raw_stage + 1024;
-  auto kern = gemm_kernel<ENC, TT, RT>;
+  auto kern = gemm_kernel<ENC, TT, RT, KS>;
   static std::mutex mu;
   static bool configured = false;
   {
@@ -891,9 +983,13 @@ Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
   static const int forced_rows = env_int("ULLM_CUDA_GEMM_ROWS");
   const uint32_t tiles_m = (a.m + pl.tt - 1) / pl.tt;
   if (a.encoding == FP8 && pl.tt == 256) {
-    // measured: with two 96 KB stages the 256-row tile waits on its loads more than it saves (0.93 vs
-    // 1.06 PFLOP/s at 2048 x 14336 x 4096), so it is opt-in
-    pl.rt = forced_rows == 256 ? 2 : 1;
+    // Measured (PFLOP/s, 128 vs 256 rows): 1.06 / 0.89 at 2048 x 14336 x 4096, 1.03 / 1.17 at 2048 x 4096 x 14336,
+    // 1.16 / 1.27 at 4096 x 57344 x 8192.  The 256-row accumulators fill tensor memory, so that tile's epilogue
+    // does not overlap the next tile's MMAs: it pays off once K is long enough to amortise it.
+    const uint32_t tiles2 = ((a.n + 2 * BM - 1) / (2 * BM)) * tiles_m;
+    pl.rt = (a.k >= 8192 && tiles2 >= sms) ? 2 : 1;
+    if (forced_rows == 128) pl.rt = 1;
+    if (forced_rows == 256) pl.rt = 2;
   }
   const uint32_t tiles_n = (a.n + pl.rt * BM - 1) / (pl.rt * BM);
   const uint32_t kb = a.k / BKB;
@@ -965,6 +1061,9 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   p.partial = pl.sk_ctas == 0 ? nullptr : reinterpret_cast<float *>(scratch + pl.off_partial);
   p.tile_counters = ctx->tile_counters;
   p.flags = ctx->device_flags;
+  static const bool trace = env_int("ULLM_CUDA_GEMM_TRACE") == 1;
+  if (trace && cudaMalloc(reinterpret_cast<void **>(&p.trace), 16 * sizeof(unsigned long long)) == cudaSuccess)
+    (void)cudaMemset(p.trace, 0, 16 * sizeof(unsigned long long));
   if (pair) {  // gate|up to scratch as bf16, combined afterwards
     p.y = scratch + pl.off_pair;
     p.y_stride = a.n;
@@ -975,7 +1074,9 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
     p.y_dtype = a.y_dtype;
   }
   CUtensorMap wmap, xmap;
-  if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding) || !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)pl.tt))
+  static const bool whole_k_stage = env_int("ULLM_CUDA_GEMM_STAGE_K") == 128;
+  const uint32_t ks = (a.encoding == FP8 && pl.tt == 256 && !whole_k_stage) ? 64u : 128u;
+  if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding, ks) || !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)pl.tt, ks))
     return cudaErrorInvalidValue;
   if (a.encoding == AQ4) {
     switch (pl.tt) {
@@ -991,13 +1092,27 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
       case 64: e = launch_tile<FP8, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
       case 128: e = launch_tile<FP8, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
       default:
-        e = pl.rt == 2 ? launch_tile<FP8, 256, 2>(stream, wmap, xmap, p, pl.grid)
-                       : launch_tile<FP8, 256, 1>(stream, wmap, xmap, p, pl.grid);
+        if (ks == 64)
+          e = pl.rt == 2 ? launch_tile<FP8, 256, 2, 64>(stream, wmap, xmap, p, pl.grid)
+                         : launch_tile<FP8, 256, 1, 64>(stream, wmap, xmap, p, pl.grid);
+        else
+          e = pl.rt == 2 ? launch_tile<FP8, 256, 2>(stream, wmap, xmap, p, pl.grid)
+                         : launch_tile<FP8, 256, 1>(stream, wmap, xmap, p, pl.grid);
         break;
     }
   }
   if (e != cudaSuccess) return e;
   ++*launches;
+  if (p.trace != nullptr) {
+    // ULLM_CUDA_GEMM_TRACE=1: cycles CTA 0's role leaders spent in each state (this path synchronises)
+    unsigned long long h[16];
+    if (cudaStreamSynchronize(stream) == cudaSuccess && cudaMemcpy(h, p.trace, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess)
+      std::fprintf(stderr,
+                   "gemm trace m=%u n=%u k=%u: tma work %llu wait-empty %llu | mma work %llu wait-acc-empty %llu wait-a-full %llu "
+                   "wait-full %llu | conv work %llu wait-raw %llu wait-empty %llu | epi work %llu wait-acc-full %llu\n",
+                   a.m, a.n, a.k, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[10]);
+    (void)cudaFree(p.trace);
+  }
   if (pair) {
     dim3 g2((a.n / 2 + 255) / 256 > 64 ? 64 : (a.n / 2 + 255) / 256, a.m);
     swiglu_kernel<<<g2, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(scratch + pl.off_pair), a.n / 2,
@@ -1028,9 +1143,17 @@ bool gemm_supports(const Context *, const LinearArgs &a, const char **why) {
 }
 
 // Scratch owned by the context: grows on demand, reused by every GEMM on that context.
-static cudaError_t ensure_scratch(const Context *cctx, size_t bytes, void **out) {
+static cudaError_t ensure_scratch(const Context *cctx, cudaStream_t stream, size_t bytes, void **out) {
   Context *ctx = const_cast<Context *>(cctx);
   std::lock_guard<std::mutex> g(ctx->mutex);
+  if ((ctx->tile_counters == nullptr || ctx->scratch_bytes < bytes) && stream != nullptr) {
+    // an allocation would invalidate a stream capture in progress: refuse instead (run the same linear once
+    // outside the capture, or create the stack, which reserves its scratch, before capturing)
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(stream, &cs);
+    if (e != cudaSuccess) return e;
+    if (cs != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
+  }
   if (ctx->tile_counters == nullptr) {
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&ctx->tile_counters), kMaxCounterTiles * sizeof(uint32_t));
     if (e != cudaSuccess) return e;
@@ -1054,7 +1177,7 @@ static cudaError_t ensure_scratch(const Context *cctx, size_t bytes, void **out)
 
 cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes) {
   void *unused = nullptr;
-  return ensure_scratch(ctx, bytes, &unused);
+  return ensure_scratch(ctx, nullptr, bytes, &unused);
 }
 
 size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a) { return make_plan(ctx, a, true).bytes; }
@@ -1098,7 +1221,7 @@ int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const Li
 int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
   const Plan pl = make_plan(ctx, a, true);
   void *s = nullptr;
-  *err = ensure_scratch(ctx, pl.bytes, &s);
+  *err = ensure_scratch(ctx, stream, pl.bytes, &s);
   if (*err != cudaSuccess) return -1;
   int launches = 0;
   *err = run_plan(ctx, stream, a, pl, static_cast<uint8_t *>(s), &launches);

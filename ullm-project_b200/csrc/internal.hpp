@@ -279,6 +279,12 @@ int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const Li
 size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a);
 cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes);
 bool gemm_supports(const Context *ctx, const LinearArgs &a, const char **why);
+// Kernel behind ULLM_CUDA_KERNEL_AUTO when both serve the shape.  Measured on weights larger than L2: the
+// tensor-core path streams FP8 weights faster than the CUDA-core matvec from two tokens on (5.2 vs 3.7 TB/s
+// at M=2, 2.7 vs 0.84 at M=8); for AQ4 it wins from five tokens on (1.6 vs 1.0 TB/s at M=8, 1.6 vs 1.9 at M=4).
+inline bool auto_prefers_gemm(const LinearArgs &a) {
+  return a.encoding == ULLM_CUDA_ENCODING_FP8_CHANNEL ? a.m >= 2 : a.m >= 5;
+}
 
 int launch_prologue(cudaStream_t stream, const LinearArgs &a, void *x_bf16_out, cudaError_t *err);
 

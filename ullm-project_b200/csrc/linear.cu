@@ -1,5 +1,5 @@
 // The quantised linear op behind the C ABI: argument validation, kernel selection
-// (decode matvec for M <= 8, tcgen05 GEMM otherwise) and the submit -> wait shape.
+// (CUDA-core matvec for one token, or up to four with AQ4; tcgen05 GEMM otherwise) and the submit -> wait shape.
 //
 // Reference anchors:
 //   capability query before execution     crates/ullm-core/src/backend.rs:5-24 (Backend::supports)
@@ -91,7 +91,8 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   const bool mv = matvec_supports(a, &why_mv);
   const bool gm = gemm_supports(ctx, a, &why_gemm);
   uint32_t kernel = desc->kernel;
-  if (kernel == ULLM_CUDA_KERNEL_AUTO) kernel = mv ? ULLM_CUDA_KERNEL_MATVEC : (gm ? ULLM_CUDA_KERNEL_GEMM : 0u);
+  if (kernel == ULLM_CUDA_KERNEL_AUTO)
+    kernel = (mv && !(gm && auto_prefers_gemm(a))) ? ULLM_CUDA_KERNEL_MATVEC : (gm ? ULLM_CUDA_KERNEL_GEMM : 0u);
   if (kernel == ULLM_CUDA_KERNEL_MATVEC && !mv) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "matvec: %s", why_mv);
   if (kernel == ULLM_CUDA_KERNEL_GEMM && !gm) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "gemm: %s", why_gemm);
   if (kernel == 0u)

@@ -239,7 +239,10 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
     if (L.row_parallel) ++site;
     const char *reason = "";
     int n;
-    if (matvec_supports(a, &reason)) {
+    // the fused all-reduce lives in the matvec kernels; without it the faster kernel for the token count runs
+    const char *reason_gemm = "";
+    const bool mv = matvec_supports(a, &reason);
+    if (mv && (push || !(gemm_supports(st->ctx, a, &reason_gemm) && auto_prefers_gemm(a)))) {
       n = launch_matvec(st->ctx, s, a, err);
     } else if (gemm_supports(st->ctx, a, &reason)) {
       n = launch_gemm(st->ctx, s, a, err);
@@ -527,7 +530,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   }
 
   // ---- reserve the GEMM path's scratch for the largest step (it cannot grow during capture) ----
-  if (d.max_tokens > 8) {
+  if (d.max_tokens > 1) {
     size_t need = 0;
     // the need is not monotone in the token count (narrow tiles split K more ways): try every tile width
     for (const StackLinear &L : S->linears) {
