@@ -238,7 +238,6 @@ struct PushIn {        // consumer side
   const uint8_t *local_base;
   uint64_t slot_off[2];
   uint64_t slot_stride;
-  uint8_t *reduced;               // local {sum, tag} pairs: each CTA sums a 1/grid share of the ranks' slots
                                   // into it, then every CTA stages from it (so the ranks' slots are read once
                                   // per GPU, not once per CTA)
   const uint32_t *step_counter;

@@ -120,65 +120,60 @@ __device__ __forceinline__ void poll_pairs(const Params &p, const uint4 *src, ui
   }
 }
 
-// fused all-reduce, consumer half, first stage: this CTA sums its share of the ranks' slots (pairs of
-// values, in rank order: deterministic) and publishes {sum, tag} pairs for all CTAs of this GPU.
-template <int T>
-__device__ __forceinline__ void reduce_share(const Params &p, uint32_t rows) {
-  const uint32_t use_global = *p.pi.step_counter * p.pi.uses_per_step + p.pi.use;
-  const uint32_t want = use_global + 1u;
-  const uint32_t units = rows * p.k / 2;  // one unit = two values = one 16-byte word of pairs
-  const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u];
-  for (uint32_t u = blockIdx.x + threadIdx.x * gridDim.x; u < units; u += gridDim.x * T) {
-    float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
-      if (r < p.pi.tp) {
-        uint4 q[1];
-        poll_pairs<1>(p, reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride) + u, want, q);
-        s0 += __uint_as_float(q[0].x);
-        s1 += __uint_as_float(q[0].z);
-      }
-    }
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(reinterpret_cast<uint4 *>(p.pi.reduced) + u),
-                 "r"(__float_as_uint(s0)), "r"(want), "r"(__float_as_uint(s1)), "r"(want)
-                 : "memory");
-  }
-}
-
 // x[m][k .. k+8) (k % 8 == 0, k + 8 <= row length) as eight packed bf16 values; fp32
 // inputs are rounded to bf16 here (the op is defined on bf16 activations).
-template <int MODE>
+template <int MODE, bool PAIR = false>
 __device__ __forceinline__ uint4 load8_packed(const Params &p, uint32_t m, uint32_t k) {
   uint32_t w[4];
   if (MODE == kModePushIn) {
-    // fused all-reduce, consumer half, second stage: read the rank-summed values this GPU's CTAs
-    // have published as {sum, tag} pairs (see reduce_share); a pair that is not there yet is re-read.
+    // fused all-reduce, consumer half: sum the ranks' slots, {value, tag} pairs, in rank order (deterministic).
+    // With PAIR (kernels that have the registers: 640 threads or fewer) two ranks' words are requested together,
+    // so a unit costs tp/2 round trips to L2 rather than tp; a word whose tag is not there yet is polled on its own.
     const uint32_t use_global = *p.pi.step_counter * p.pi.uses_per_step + p.pi.use;
     const uint32_t want = use_global + 1u;
+    const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u] + ((uint64_t)m * p.k + k) * 8;
     float v[8];
-    if (p.pi.reduced != nullptr) {
-      const uint4 *src = reinterpret_cast<const uint4 *>(p.pi.reduced + ((uint64_t)m * p.k + k) * 8);
-      uint4 q[4];
-      poll_pairs<4>(p, src, want, q);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(q[i].x);
-        v[2 * i + 1] = __uint_as_float(q[i].z);
-      }
-    } else {
-      // few ranks: every CTA sums the ranks' slots itself (one stage, no local round trip)
-      const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u] + ((uint64_t)m * p.k + k) * 8;
+    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; r += PAIR ? 2 : 1) {
+      if (r < p.pi.tp) {
+        const uint4 *s0 = reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride);
+        const bool two = PAIR && r + 1 < p.pi.tp;
+        const uint4 *s1 = reinterpret_cast<const uint4 *>(base + (uint64_t)(two ? r + 1 : r) * p.pi.slot_stride);
+        uint4 q0[4], q1[4];
 #pragma unroll
-      for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
-        if (r < p.pi.tp) {
-          uint4 q[4];
-          poll_pairs<4>(p, reinterpret_cast<const uint4 *>(base + (uint64_t)r * p.pi.slot_stride), want, q);
+        for (int i = 0; i < 4; ++i)
+          asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(q0[i].x), "=r"(q0[i].y), "=r"(q0[i].z), "=r"(q0[i].w)
+                       : "l"(s0 + i)
+                       : "memory");
+        if (PAIR) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(q1[i].x), "=r"(q1[i].y), "=r"(q1[i].z), "=r"(q1[i].w)
+                         : "l"(s1 + i)
+                         : "memory");
+        }
+        bool ok0 = true, ok1 = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          ok0 = ok0 && q0[i].y == want && q0[i].w == want;
+          if (PAIR) ok1 = ok1 && q1[i].y == want && q1[i].w == want;
+        }
+        if (!ok0) poll_pairs<4>(p, s0, want, q0);
+        if (PAIR && !ok1) poll_pairs<4>(p, s1, want, q1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[2 * i] += __uint_as_float(q0[i].x);
+          v[2 * i + 1] += __uint_as_float(q0[i].z);
+        }
+        if (two) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            v[2 * i] += __uint_as_float(q[i].x);
-            v[2 * i + 1] += __uint_as_float(q[i].z);
+            v[2 * i] += __uint_as_float(q1[i].x);
+            v[2 * i + 1] += __uint_as_float(q1[i].z);
           }
         }
       }
@@ -322,7 +317,6 @@ template <int M, int T, int CACHE, uint32_t ENC, int MODE>
 __device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq, float *red) {
   const uint32_t tid = threadIdx.x;
   const uint32_t nchunks = p.k / 8, padded = p.k_pad / 8;
-  if (MODE == kModePushIn && p.pi.reduced != nullptr) reduce_share<T>(p, M);
   const bool rms = p.prologue == ULLM_CUDA_PROLOGUE_RMSNORM;
   const bool cached = rms && nchunks <= (uint32_t)(CACHE * T);
   uint4 cache[M][CACHE];
@@ -339,14 +333,14 @@ __device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq,
         const uint32_t c = tid + i * T;
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          cache[m][i] = c < nchunks ? load8_packed<MODE>(p, m, c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          cache[m][i] = c < nchunks ? load8_packed<MODE, (T <= 640)>(p, m, c * 8) : make_uint4(0u, 0u, 0u, 0u);
           ss[m] += sumsq8(cache[m][i]);
         }
       }
     } else {
       for (uint32_t c = tid; c < nchunks; c += T)
 #pragma unroll
-        for (int m = 0; m < M; ++m) ss[m] += sumsq8(load8_packed<MODE>(p, m, c * 8));
+        for (int m = 0; m < M; ++m) ss[m] += sumsq8(load8_packed<MODE, (T <= 640)>(p, m, c * 8));
     }
 #pragma unroll
     for (int m = 0; m < M; ++m) {
@@ -390,7 +384,7 @@ __device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq,
     for (uint32_t c = tid; c < padded; c += T) {
 #pragma unroll
       for (int m = 0; m < M; ++m)
-        emit(c, m, c < nchunks ? load8_packed<MODE>(p, m, c * 8) : make_uint4(0u, 0u, 0u, 0u));
+        emit(c, m, c < nchunks ? load8_packed<MODE, (T <= 640)>(p, m, c * 8) : make_uint4(0u, 0u, 0u, 0u));
     }
   }
   __syncthreads();

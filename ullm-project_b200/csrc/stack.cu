@@ -68,7 +68,6 @@ struct Stack {
   bool push = false;
   static constexpr uint32_t kRing = 4;
   uint64_t ring_slot_off[kRing][2] = {};
-  uint64_t ring_reduced_off[kRing] = {};
   uint64_t step_counter_off = 0;        // local word bumped once per step
   uint64_t slot_stride = 0;
   uint32_t sites = 0;                   // row-parallel linears per step
@@ -210,12 +209,6 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
         a.push_in.slot_off[0] = st->ring_slot_off[r][0];
         a.push_in.slot_off[1] = st->ring_slot_off[r][1];
         a.push_in.slot_stride = st->slot_stride;
-        // Every CTA sums the ranks' slots itself (one stage: measured faster at 2 and 4 ranks, 8.46 vs 9.17 ms
-        // and 6.10 vs 7.15 ms per 70B step).  ULLM_CUDA_PUSH_TWO_STAGE=1 selects the variant that sums the
-        // slots once per GPU, each CTA a share, and lets every CTA read the published sums.
-        static const char *two_stage_env = std::getenv("ULLM_CUDA_PUSH_TWO_STAGE");
-        const bool two_stage = two_stage_env != nullptr && two_stage_env[0] == '1';
-        a.push_in.reduced = two_stage ? local + st->ring_reduced_off[r] : nullptr;
         a.push_in.step_counter = counter;
         a.push_in.uses_per_step = uses_of(r);
         a.push_in.use = (site - 1) / Stack::kRing;
@@ -520,8 +513,6 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
         S->ring_slot_off[r][par] = off;
         off += S->slot_stride * t;
       }
-      S->ring_reduced_off[r] = off;
-      off += S->slot_stride;
     }
     S->step_counter_off = off;
     off += 256;
