@@ -650,12 +650,19 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t groups = p.k / 128;
         const uint32_t row = n0 + row_in_tile;
         const __half *srow = static_cast<const __half *>(p.scales) + (uint64_t)(row < p.n ? row : 0) * groups + sg.kb0;
+        // the scales of a batch are requested one batch ahead, so their latency is off the drain's critical path
+        float sc_next[GB];
+#pragma unroll
+        for (uint32_t j = 0; j < GB; ++j) sc_next[j] = (j < sg.nkb && row < p.n) ? __half2float(srow[j]) : 0.0f;
         for (uint32_t g = 0; g < sg.nkb && ok; ++batch) {
           const uint32_t cnt = sg.nkb - g < GB ? sg.nkb - g : GB;  // groups in this batch
           const uint32_t buf = batch % NB, use = batch / NB;
           float sc[GB];
 #pragma unroll
-          for (uint32_t j = 0; j < GB; ++j) sc[j] = (j < cnt && row < p.n) ? __half2float(srow[g + j]) : 0.0f;
+          for (uint32_t j = 0; j < GB; ++j) {
+            sc[j] = sc_next[j];
+            sc_next[j] = (g + GB + j < sg.nkb && row < p.n) ? __half2float(srow[g + GB + j]) : 0.0f;
+          }
           lap.lap(9);
           ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
           lap.lap(10);
