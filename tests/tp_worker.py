@@ -46,9 +46,13 @@ def main():
     err = float(np.sqrt(np.mean((y - mine) ** 2)) / np.sqrt(np.mean(mine ** 2)))
     assert err < 0.02, err
     _, launches = st.stats()
-    if m <= 8:  # matvec path: one kernel per linear; the sum over ranks is fused into them (peer-memory
-        # push), or one ncclAllReduce after O and after down when peer mapping is unavailable / switched off
-        assert launches in (shape.layers * 4 + 2, shape.layers * 4 + 1 + shape.layers * 2)  # push: + the step tick
+    # one kernel per linear on the matvec path (the sum over ranks fused into them, plus the step tick), up to
+    # three on the tensor-core path (activation planes, GEMM, SwiGLU), plus one ncclAllReduce after O and after
+    # down when the sum is not fused
+    linears = shape.layers * 4 + 1
+    assert linears + 1 <= launches <= 3 * linears + 2 * shape.layers, launches
+    if m == 1 and not nccl_only:
+        assert launches in (linears + 1, linears + 2 * shape.layers), launches
     # the first row-parallel sum, checked at the stated tolerance: O(qkv) summed over ranks
     info = st.linear_info(0, U.LINEAR_O)
     o_sum = q.download(info.last_output, (m, shape.hidden), np.float32)
