@@ -448,10 +448,19 @@ def main():
                                  ("fp8_m8_k4096_n14336", U.ENCODING_FP8_CHANNEL, 14336, 4096, 8),
                                  ("fp8_m1_k8192_n57344", U.ENCODING_FP8_CHANNEL, 57344, 8192, 1),
                                  ("aq4_m1_k4096_n28672", U.ENCODING_AQ4, 28672, 4096, 1)):
-            r = time_matvec_extra(U, ctx, q, e, n, k, m, reps=20)
+            r = time_matvec_extra(U, ctx, q, e, n, k, m, reps=20, kernel=U.KERNEL_AUTO)
             r["frac_of_peak"] = r["gbs"] / peak
             extra[name] = r
         line["matvec"] = extra
+        burst, _, _ = tensor_peaks()
+        gemms = {}
+        for name, e, mm, n, k in (("aq4_m2048_k4096_n14336", U.ENCODING_AQ4, 2048, 14336, 4096),
+                                  ("aq4_m2048_k14336_n4096", U.ENCODING_AQ4, 2048, 4096, 14336),
+                                  ("fp8_m2048_k4096_n14336", U.ENCODING_FP8_CHANNEL, 2048, 14336, 4096)):
+            r = time_gemm(U, ctx, q, e, mm, n, k, reps=10)
+            r["frac_of_peak"] = r["tflops"] / burst
+            gemms[name] = r
+        line["gemm"] = gemms
         one_pass, elems, threads = cpu_sample(shape, enc, B)
         one_pass()
         passes, spent = [], 0.0

@@ -61,7 +61,6 @@ constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
 constexpr uint32_t A_BYTES = BM * BKB;        // e4m3 operand tile
 constexpr uint32_t RAW_BYTES = BM * BKB / 2;  // packed nibble tile
 constexpr int MAX_STAGES = 8, MAX_RAW = 8;
-static_assert(MAX_STAGES % kConvWarps == 0 && MAX_RAW % kConvWarps == 0, "ring lengths are multiples of the converter warps");
 constexpr uint32_t kFlagGemmWait = 2u;
 constexpr uint64_t kWaitLimitNs = 20ull * 1000ull * 1000ull * 1000ull;
 constexpr uint32_t kMaxCounterTiles = 1024;  // phase-2 tiles: fewer than the SM count
@@ -351,12 +350,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     last_flag = 0u;
     for (uint32_t s = 0; s < NS; ++s) {
       mbar_init(full(s), 1u);                       // the TMA thread's expect_tx
-      mbar_init(a_full(s), 1u);                     // the converter warp that owns the k-block
+      mbar_init(a_full(s), (uint32_t)kConvWarps);   // one arrival per converter warp
       mbar_init(empty(s), 1u);                      // tcgen05.commit
     }
     for (uint32_t s = 0; s < RS; ++s) {
       mbar_init(raw_full(s), 1u);
-      mbar_init(raw_empty(s), 1u);
+      mbar_init(raw_empty(s), (uint32_t)kConvWarps);
     }
     for (uint32_t b = 0; b < 4; ++b) {
       mbar_init(acc_full(b), 1u);                     // tcgen05.commit
@@ -500,20 +499,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp >= kConvWarp0 && warp < kConvWarp0 + kConvWarps) {
     // ---- AQ4: nibble tile -> e4m3 operand tile ------------------------------------------------
-    // Converter warp w owns the k-blocks whose running number is w modulo the number of converter warps and
-    // converts all 128 rows of them, so a warp's shared-memory latencies and its proxy fence overlap the
-    // other warps' work on the neighbouring k-blocks.  Both rings are multiples of that number long, so a
-    // warp always meets the same slots and waits on each of their phases in turn (a parity wait that skipped
-    // a phase would pass on the wrong one).
+    // The four converter warps share every k-block: thread t takes items t, t+128, t+256, t+384 of the 512
+    // (row, 16-byte chunk) items, so a warp's loads are 512 contiguous bytes and its stores hit every bank once.
+    // Item (row, c): the 16 bytes c of the row's 64 = k 32c .. 32c+31; the even elements of those 32 go to
+    // operand chunk 2c, the odd ones to chunk 2c+1 (the activation planes use the same order).
     if (ENC == AQ4) {
-      const uint32_t cw = warp - kConvWarp0;
-      uint32_t number = 0;  // running k-block number over all segments
+      const uint32_t ct = threadIdx.x - kConvWarp0 * 32;
+      uint32_t slot = 0, round = 0, rslot = 0, rround = 0;
       bool ok = true;
-      Lap lap(p.trace, cw == 0 && lane == 0);
+      Lap lap(p.trace, ct == 0);
       while (ok && walk.next(&sg)) {
-        for (uint32_t i = 0; i < sg.nkb; ++i, ++number) {
-          if (number % kConvWarps != cw) continue;
-          const uint32_t slot = number % NS, round = number / NS, rslot = number % RS, rround = number / RS;
+        for (uint32_t i = 0; i < sg.nkb; ++i) {
           lap.lap(6);
           if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags)) {
             ok = false;
@@ -529,36 +525,31 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int r = 0; r < RT; ++r) {
             const uint32_t raw_addr = raw0 + (rslot * RT + r) * RAW_BYTES;
             const uint32_t a_addr = smem0 + slot * STAGE_BYTES + r * A_BYTES;
-#pragma unroll 1
-            for (int jb = 0; jb < 16; jb += 4) {
-              uint4 q[4];
+            uint4 q[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t addr = raw_addr + (lane + 32u * (jb + j)) * 16u;
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
-                             : "r"(addr));
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr = raw_addr + (ct + 128u * j) * 16u;
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
+                           : "r"(addr));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t row = (ct >> 2) + 32u * j, c = ct & 3u;
+              const uint32_t a_row = a_addr + row * 128u;
+              const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+              uint32_t ev[4], od[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                ev[t] = nibble_bytes_to_e4m3(w[t] & 0x0f0f0f0fu);
+                od[t] = nibble_bytes_to_e4m3((w[t] >> 4) & 0x0f0f0f0fu);
               }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                // item (row, c): the 16 bytes c of the row's 64 = k 32c .. 32c+31; the even elements of those 32
-                // go to operand chunk 2c, the odd ones to chunk 2c+1 (the activation planes use the same order)
-                const uint32_t row = (lane >> 2) + 8u * (jb + j), c = lane & 3u;
-                const uint32_t a_row = a_addr + row * 128u;
-                const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-                uint32_t ev[4], od[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  ev[t] = nibble_bytes_to_e4m3(w[t] & 0x0f0f0f0fu);
-                  od[t] = nibble_bytes_to_e4m3((w[t] >> 4) & 0x0f0f0f0fu);
-                }
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c) ^ (row & 7u)) << 4)),
-                             "r"(ev[0]), "r"(ev[1]), "r"(ev[2]), "r"(ev[3])
-                             : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c + 1u) ^ (row & 7u)) << 4)),
-                             "r"(od[0]), "r"(od[1]), "r"(od[2]), "r"(od[3])
-                             : "memory");
-              }
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c) ^ (row & 7u)) << 4)),
+                           "r"(ev[0]), "r"(ev[1]), "r"(ev[2]), "r"(ev[3])
+                           : "memory");
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + (((2u * c + 1u) ^ (row & 7u)) << 4)),
+                           "r"(od[0]), "r"(od[1]), "r"(od[2]), "r"(od[3])
+                           : "memory");
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
@@ -566,6 +557,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) {
             mbar_arrive(a_full(slot));
             mbar_arrive(raw_empty(rslot));
+          }
+          if (++slot == NS) {
+            slot = 0;
+            ++round;
+          }
+          if (++rslot == RS) {
+            rslot = 0;
+            ++rround;
           }
         }
       }
@@ -913,17 +912,10 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
   size_t ns = 0, rs = 0;
   if (ENC == AQ4) {
-    // A converter warp must see every phase of the barriers it waits on, so it keeps the same slots for the
-    // whole kernel: both ring lengths are multiples of the number of converter warps.
-    const size_t room = budget;
-    if (8 * stage + 4 * raw_stage <= room) {
-      ns = 8;
-      rs = 8 * stage + 8 * raw_stage <= room ? 8 : 4;
-    } else {
-      ns = 4;
-      rs = 4 * stage + 8 * raw_stage <= room ? 8 : 4;
-    }
-    if (ns * stage + rs * raw_stage > room) return cudaErrorInvalidConfiguration;
+    ns = (budget - 3 * raw_stage) / stage;
+    if (ns > MAX_STAGES) ns = MAX_STAGES;
+    rs = (budget - ns * stage) / raw_stage;
+    if (rs > MAX_RAW) rs = MAX_RAW;
   } else {
     ns = budget / stage;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
