@@ -45,7 +45,6 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
-#include <cstdio>
 #include <cstdlib>
 
 namespace ullm {
@@ -80,7 +79,6 @@ struct GemmParams {
   float *partial;           // [range][head, tail][row block][TT][128] fp32
   uint32_t *tile_counters;  // one per phase-2 tile, zero between launches
   uint32_t *flags;
-  unsigned long long *trace;  // diagnostic: CTA 0 adds up the cycles its roles spend waiting (null: off)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -268,22 +266,6 @@ struct Walker {
   }
 };
 
-// Diagnostic stopwatch: cycles between construction/lap() calls are added to trace[slot] by CTA 0's role leaders.
-struct Lap {
-  unsigned long long *trace;
-  long long t;
-  __device__ Lap(unsigned long long *tr, bool leader) : trace(leader && blockIdx.x == 0 ? tr : nullptr), t(0) {
-    if (trace) t = clock64();
-  }
-  __device__ void lap(int slot) {
-    if (trace) {
-      const long long now = clock64();
-      trace[slot] += (unsigned long long)(now - t);
-      t = now;
-    }
-  }
-};
-
 // Four bytes, each holding a nibble u = q + 8 (0..15): each becomes the e4m3 byte of q * 2^-9, that is
 // |q| with the sign in bit 7 (|q| <= 8 sits in the linear part of e4m3, where the byte value is the magnitude).
 __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
@@ -382,17 +364,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t slot = 0, round = 0;
       bool ok = true;
-      Lap lap(p.trace, true);
       while (ok && walk.next(&sg)) {
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
         for (uint32_t i = 0; i < sg.nkb * SUBS; ++i) {
-          lap.lap(0);
           if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
             ok = false;
             break;
           }
-          lap.lap(1);
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES;
           const int kx = (int)(sg.kb0 * BKB + i * KS);
           mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_STAGE : 0u) + 2 * B_BYTES);
@@ -415,15 +394,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc = instr_desc_e4m3((int)MMA_N);
       uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
-      Lap lap(p.trace, true);
       while (ok && walk.next(&sg)) {
         uint32_t buf = 0;
         if (ENC == FP8) {
           buf = seg % NB;
           const uint32_t use = seg / NB;
-          lap.lap(2);
           if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
-          lap.lap(3);
         }
         for (uint32_t i = 0; i < sg.nkb * SUBS && ok; ++i) {
           uint32_t fresh = i == 0 ? 1u : 0u;
@@ -431,15 +407,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             buf = batch % NB;
             const uint32_t use = batch / NB;
             fresh = 1u;
-            lap.lap(2);
             if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
-            lap.lap(3);
             ok = ok && mbar_wait(a_full(slot), round & 1u, &abort_flag, p.flags);
-            lap.lap(4);
           }
-          lap.lap(2);
           ok = ok && mbar_wait(full(slot), round & 1u, &abort_flag, p.flags);
-          lap.lap(5);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
@@ -507,37 +478,36 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t ct = threadIdx.x - kConvWarp0 * 32;
       uint32_t slot = 0, round = 0, rslot = 0, rround = 0;
       bool ok = true;
-      Lap lap(p.trace, ct == 0);
       while (ok && walk.next(&sg)) {
         for (uint32_t i = 0; i < sg.nkb; ++i) {
-          lap.lap(6);
           if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags)) {
             ok = false;
             break;
           }
-          lap.lap(7);
+          // the nibbles are requested before the wait for a free operand tile, so that wait hides their latency
+          uint4 q[RT][4];
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr = raw0 + (rslot * RT + r) * RAW_BYTES + (ct + 128u * j) * 16u;
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(q[r][j].x), "=r"(q[r][j].y), "=r"(q[r][j].z), "=r"(q[r][j].w)
+                           : "r"(addr));
+            }
+          }
           if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
             ok = false;
             break;
           }
-          lap.lap(8);
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
-            const uint32_t raw_addr = raw0 + (rslot * RT + r) * RAW_BYTES;
             const uint32_t a_addr = smem0 + slot * STAGE_BYTES + r * A_BYTES;
-            uint4 q[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t addr = raw_addr + (ct + 128u * j) * 16u;
-              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w)
-                           : "r"(addr));
-            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t row = (ct >> 2) + 32u * j, c = ct & 3u;
               const uint32_t a_row = a_addr + row * 128u;
-              const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+              const uint32_t w[4] = {q[r][j].x, q[r][j].y, q[r][j].z, q[r][j].w};
               uint32_t ev[4], od[4];
 #pragma unroll
               for (int t = 0; t < 4; ++t) {
@@ -584,7 +554,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr uint64_t PART = (uint64_t)RT * TT * BM;  // floats of one partial tile
     uint32_t seg = 0, batch = 0;
     bool ok = true;
-    Lap lap(p.trace, e == 0 && lane == 0);
     while (walk.next(&sg)) {
       uint32_t n0, m0;
       tile_origin(sg.tile, &n0, &m0);
@@ -613,9 +582,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       if (ENC == FP8) {
         const uint32_t buf = seg % NB, use = seg / NB;
-        lap.lap(9);
         ok = ok && mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
-        lap.lap(10);
         if (ok) {
           tc_fence_after();
           if (active) {
@@ -650,45 +617,72 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t row = n0 + row_in_tile;
         const __half *srow = static_cast<const __half *>(p.scales) + (uint64_t)(row < p.n ? row : 0) * groups + sg.kb0;
         // the scales of a batch are requested one batch ahead, so their latency is off the drain's critical path
-        float sc_next[GB];
+        if constexpr (GB == 1) {
+          // one group per hand-off: the next group's scale is requested while this one is drained
+          float sc_next = row < p.n ? __half2float(srow[0]) : 0.0f;
+          for (uint32_t g = 0; g < sg.nkb && ok; ++g, ++batch) {
+            const uint32_t buf = batch % NB, use = batch / NB;
+            const float sc = sc_next;
+            if (g + 1 < sg.nkb && row < p.n) sc_next = __half2float(srow[g + 1]);
+            ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+            if (!ok) break;
+            tc_fence_after();
+            if (active) {
 #pragma unroll
-        for (uint32_t j = 0; j < GB; ++j) sc_next[j] = (j < sg.nkb && row < p.n) ? __half2float(srow[j]) : 0.0f;
-        for (uint32_t g = 0; g < sg.nkb && ok; ++batch) {
-          const uint32_t cnt = sg.nkb - g < GB ? sg.nkb - g : GB;  // groups in this batch
-          const uint32_t buf = batch % NB, use = batch / NB;
-          float sc[GB];
+              for (int c = 0; c < COLS; c += CH) {
+                uint32_t v[CH], v2[CH];
+                tmem_ld(lane_addr + buf * BUF_COLS + col0 + c, v);
+                if (NCAT) tmem_ld(lane_addr + buf * BUF_COLS + TT + col0 + c, v2);
+                tmem_ld_wait();
 #pragma unroll
-          for (uint32_t j = 0; j < GB; ++j) {
-            sc[j] = sc_next[j];
-            sc_next[j] = (g + GB + j < sg.nkb && row < p.n) ? __half2float(srow[g + GB + j]) : 0.0f;
+                for (int i = 0; i < CH; ++i)
+                  acc[c + i] = fmaf(sc, NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]), acc[c + i]);
+              }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take a later group
           }
-          lap.lap(9);
-          ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
-          lap.lap(10);
-          if (!ok) break;
-          tc_fence_after();
-          if (active) {
+        } else {
+          // a batch of GB groups per hand-off (narrow tiles); the scales of a batch are requested one batch ahead
+          float sc_next[GB];
+#pragma unroll
+          for (uint32_t j = 0; j < GB; ++j) sc_next[j] = (j < sg.nkb && row < p.n) ? __half2float(srow[j]) : 0.0f;
+          for (uint32_t g = 0; g < sg.nkb && ok; ++batch) {
+            const uint32_t cnt = sg.nkb - g < GB ? sg.nkb - g : GB;  // groups in this batch
+            const uint32_t buf = batch % NB, use = batch / NB;
+            float sc[GB];
 #pragma unroll
             for (uint32_t j = 0; j < GB; ++j) {
-              if (j < cnt) {
+              sc[j] = sc_next[j];
+              sc_next[j] = (g + GB + j < sg.nkb && row < p.n) ? __half2float(srow[g + GB + j]) : 0.0f;
+            }
+            ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+            if (!ok) break;
+            tc_fence_after();
+            if (active) {
 #pragma unroll
-                for (int c = 0; c < COLS; c += CH) {
-                  uint32_t v[CH], v2[CH];
-                  tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + col0 + c, v);
-                  if (NCAT) tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + TT + col0 + c, v2);
-                  tmem_ld_wait();
+              for (uint32_t j = 0; j < GB; ++j) {
+                if (j < cnt) {
 #pragma unroll
-                  for (int i = 0; i < CH; ++i)
-                    acc[c + i] =
-                        fmaf(sc[j], NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]), acc[c + i]);
+                  for (int c = 0; c < COLS; c += CH) {
+                    uint32_t v[CH], v2[CH];
+                    tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + col0 + c, v);
+                    if (NCAT) tmem_ld(lane_addr + buf * BUF_COLS + j * ACC_COLS + TT + col0 + c, v2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CH; ++i)
+                      acc[c + i] = fmaf(sc[j], NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]),
+                                        acc[c + i]);
+                  }
                 }
               }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take the batch after next
+            g += cnt;
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty(buf));  // this buffer may take the batch after next
-          g += cnt;
         }
         if (ok && active) {
 #pragma unroll
@@ -741,7 +735,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ++seg;
     }
-    lap.lap(9);
   }
   tc_fence_before();
   __syncthreads();
@@ -1060,9 +1053,6 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   p.partial = pl.sk_ctas == 0 ? nullptr : reinterpret_cast<float *>(scratch + pl.off_partial);
   p.tile_counters = ctx->tile_counters;
   p.flags = ctx->device_flags;
-  static const bool trace = env_int("ULLM_CUDA_GEMM_TRACE") == 1;
-  if (trace && cudaMalloc(reinterpret_cast<void **>(&p.trace), 16 * sizeof(unsigned long long)) == cudaSuccess)
-    (void)cudaMemset(p.trace, 0, 16 * sizeof(unsigned long long));
   if (pair) {  // gate|up to scratch as bf16, combined afterwards
     p.y = scratch + pl.off_pair;
     p.y_stride = a.n;
@@ -1102,16 +1092,6 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   }
   if (e != cudaSuccess) return e;
   ++*launches;
-  if (p.trace != nullptr) {
-    // ULLM_CUDA_GEMM_TRACE=1: cycles CTA 0's role leaders spent in each state (this path synchronises)
-    unsigned long long h[16];
-    if (cudaStreamSynchronize(stream) == cudaSuccess && cudaMemcpy(h, p.trace, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess)
-      std::fprintf(stderr,
-                   "gemm trace m=%u n=%u k=%u: tma work %llu wait-empty %llu | mma work %llu wait-acc-empty %llu wait-a-full %llu "
-                   "wait-full %llu | conv work %llu wait-raw %llu wait-empty %llu | epi work %llu wait-acc-full %llu\n",
-                   a.m, a.n, a.k, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[10]);
-    (void)cudaFree(p.trace);
-  }
   if (pair) {
     dim3 g2((a.n / 2 + 255) / 256 > 64 ? 64 : (a.n / 2 + 255) / 256, a.m);
     swiglu_kernel<<<g2, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(scratch + pl.off_pair), a.n / 2,
