@@ -132,3 +132,35 @@ def test_prefill_shape_on_sampled_rows(gpu):
             check(y[:, rows], o.linear(np.ascontiguousarray(x[:, :k]), oracle_dequantize(v, s, encoding)), (encoding, n, k))
             for b in (src, vals, scl, xb, yb):
                 b.close()
+
+
+def test_wide_row_tiles_and_k_split_tail_on_sampled_rows(gpu):
+    """Shapes that take the 256-weight-row tiles (FP8, K >= 8192, enough tiles for every SM) and a tail of tiles
+    cut along K: 1024 tokens, N = 9728 (38 tiles of 256 rows x 4 token tiles = 152 tiles on 148 SMs), K = 8192;
+    and 300 tokens with N = 2176, whose 34 tiles are all cut along K.  Sampled output channels against the oracle."""
+    ctx, q = gpu
+    for encoding, m, n, k in ((U.ENCODING_FP8_CHANNEL, 1024, 9728, 8192), (U.ENCODING_FP8_CHANNEL, 300, 2176, 8192),
+                              (U.ENCODING_AQ4, 300, 2176, 8192)):
+        x = o.synth_activations(SEED, 1750 + m, m, k)
+        src = ctx.alloc(n * k * 4)
+        q.synth_weights(SEED, 1760 + encoding, 0, n * k, 0.02, src.at(0))
+        vb, sb = U.weight_bytes(encoding, n, k)
+        vals, scl = ctx.alloc(vb), ctx.alloc(sb)
+        wd = U.weight_desc(encoding, n, k, vals.at(0), scl.at(0))
+        q.quantize(src.at(0), wd)
+        xb, yb = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+        q.upload(xb.at(0), o.f32_to_bf16_bits(x))
+        out = []
+        for _ in range(2):  # twice: the K-split counters must be back at zero after a launch
+            q.fill(yb.at(0), 0xC5, m * n * 2)
+            res = q.linear_submit(U.linear_desc(wd, m, xb.at(0), yb.at(0), kernel=U.KERNEL_GEMM)).wait(120000)
+            assert res.device_flags == 0
+            out.append(q.download(yb.at(0), (m, n), np.uint16))
+        assert np.array_equal(out[0], out[1])  # deterministic: partials are added in a fixed order
+        y = o.bf16_bits_to_f32(out[1])
+        rows = np.arange(3, n, 211)
+        wr = np.stack([o.synth_weights(SEED, 1760 + encoding, 1, k, row0=int(r))[0] for r in rows])
+        v, s = oracle_quantize(wr, encoding)
+        check(y[:, rows], o.linear(x, oracle_dequantize(v, s, encoding)), (encoding, m, n, k))
+        for b in (src, vals, scl, xb, yb):
+            b.close()
