@@ -50,7 +50,7 @@ def peaks():
         with open(path) as f:
             p = json.load(f)
         return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s STREAM-style copy figure; MEASURED_PEAKS.json absent)"
 
 
 class ClockSampler:
@@ -99,74 +99,233 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# DRAM traffic of the step's dominant kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum per launch),
+# captured on single-kernel workloads of full shape and scaled to the step by algorithmic bytes: the kernels read
+# each weight byte once, so traffic / algorithmic bytes is the same ratio for every matvec of the step.
+TRAFFIC_RATIO = {"fp8": 1.000, "aq4": 1.000}
+TRAFFIC_NOTE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of the matvec kernel on its full-shape single-kernel "
+                "workload (profiles/matvec_*.md), scaled to one step by algorithmic bytes")
+
+
+def stack_traffic(enc, world, algo_bytes):
+    return TRAFFIC_RATIO[enc] * algo_bytes
+
+
 def stack_algorithmic_bytes(shape, enc, batch, tp):
     """Per rank and per step: packed weights + scales + activations read and written by the linears."""
     qd, kvd = shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
     per = (lambda n, k: n * k // 2 + n * k // 64) if enc == "aq4" else (lambda n, k: n * k + 4 * n)
     # (N, K, input bytes per element, output columns, output bytes per element)
-    lin = [((qd + 2 * kvd) // tp, shape.hidden, 2, (qd + 2 * kvd) // tp, 2), (shape.hidden, qd // tp, 2, shape.hidden, 4),
+    lin = [((qd + 2 * kvd) // tp, shape.hidden, 4, (qd + 2 * kvd) // tp, 2), (shape.hidden, qd // tp, 2, shape.hidden, 4),
            (2 * shape.ffn // tp, shape.hidden, 4, shape.ffn // tp, 2), (shape.hidden, shape.ffn // tp, 2, shape.hidden, 4)]
     w = shape.layers * sum(per(n, k) for n, k, _, _, _ in lin) + per(shape.vocab // tp, shape.hidden)
     a = shape.layers * sum(batch * (k * xi + cols * yo) for n, k, xi, cols, yo in lin)
     a += batch * (shape.hidden * 4 + shape.vocab // tp * 2)
+    # glue: one bf16 RMSNorm weight vector per column-parallel linear, one fp32 residual row per row-parallel one,
+    # and the bf16 -> fp32 copy that starts the residual stream
+    a += (2 * shape.layers + 1) * shape.hidden * 2 + 2 * shape.layers * batch * shape.hidden * 4 + batch * shape.hidden * 6
     return w, a
 
 
-def cpu_sample(shape, enc, batch, seconds_hint=15.0):
-    """Times the plain-C port on ONE decoder layer (QKV, O, gate+up, down) of the same widths
-    with all host threads and scales to the whole stack by weight elements."""
-    import oracle_c as oc
+class CpuStack:
+    """The plain-C port (oracle/oracle_c.c, fp32 accumulate, OpenMP over output channels) running one decode step
+    of the linear stack on the host: per layer rmsnorm -> QKV -> O + residual -> rmsnorm -> gate|up -> swiglu ->
+    down + residual, then rmsnorm -> LM head.  All layers stream the SAME layer's weight bytes (one layer of
+    random codes is held in host memory, 0.86 GB at 70B widths: far beyond any CPU cache, so every pass still
+    streams from DRAM); the LM head has its own.  The reference project has no CPU (or any) implementation of this
+    path: this is `kind: "port"`."""
 
-    rng = np.random.default_rng(SEED)
-    qd, kvd = shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
-    lin = [(qd + 2 * kvd, shape.hidden), (shape.hidden, qd), (2 * shape.ffn, shape.hidden), (shape.hidden, shape.ffn)]
-    mats = []
-    for n, k in lin:
-        x = oc.synth_activations_bits(SEED, 5000 + k, batch, k)
-        if enc == "aq4":
-            mats.append((x, rng.integers(0x11, 0xFF, (n, k // 2), dtype=np.uint8),
-                         np.full((n, k // 128), 0.003, np.float16)))
-        else:
-            codes = rng.integers(0, 0x7E, (n, k), dtype=np.uint8) | (rng.integers(0, 2, (n, k), dtype=np.uint8) << 7)
-            mats.append((x, codes, np.full(n, 1e-4, np.float32)))
-    elems = sum(n * k for n, k in lin)
+    def __init__(self, shape, enc, batch, threads=None):
+        import oracle_c as oc
+        self.oc, self.shape, self.enc, self.batch = oc, shape, enc, batch
+        if threads is None:
+            threads = os.cpu_count() or 1  # torch.distributed.run exports OMP_NUM_THREADS=1: ask for the cores explicitly
+        oc.set_num_threads(threads)
+        self.threads = oc.num_threads()
+        rng = np.random.default_rng(SEED)
+        qd, kvd = shape.q_heads * shape.head_dim, shape.kv_heads * shape.head_dim
+        self.qd = qd
+        dims = [(qd + 2 * kvd, shape.hidden), (shape.hidden, qd), (2 * shape.ffn, shape.hidden), (shape.hidden, shape.ffn)]
 
-    def one_pass():
+        def weight(n, k):  # random codes (timing only): any byte is a valid AQ4 pair; 0xF7 keeps e4m3 off its NaN codes
+            if enc == "aq4":
+                raw = np.frombuffer(rng.bytes(n * (k // 2)), np.uint8).reshape(n, k // 2)
+                return raw, np.full((n, k // 128), 0.003, np.float16)
+            raw = np.frombuffer(rng.bytes(n * k), np.uint8).reshape(n, k) & np.uint8(0xF7)
+            return raw, np.full(n, 1e-4, np.float32)
+
+        self.layer = [weight(n, k) for n, k in dims]
+        self.head = weight(shape.vocab, shape.hidden)
+        self.layer_elems = sum(n * k for n, k in dims)
+        self.gamma = np.ones(shape.hidden, np.float32)
+        self.x = (oc.synth_activations_bits(SEED, 5000, batch, shape.hidden).astype(np.uint32) << 16).view(np.float32)
+
+    def _lin(self, x_f32, w, want):
+        import oracle as o
+        bits = o.f32_to_bf16_bits(x_f32).reshape(x_f32.shape)
+        return (self.oc.linear_aq4 if self.enc == "aq4" else self.oc.linear_fp8)(bits, w[0], w[1], want=want)
+
+    @staticmethod
+    def _rms(h, gamma):
+        r = 1.0 / np.sqrt((h.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+        return (h * r * gamma).astype(np.float32)
+
+    def layer_pass(self, h):
+        qkv = self._lin(self._rms(h, self.gamma), self.layer[0], "bf16")
+        h = h + self._lin(qkv[:, :self.qd], self.layer[1], "f32")
+        gu = self._lin(self._rms(h, self.gamma), self.layer[2], "bf16")
+        f = gu.shape[1] // 2
+        act = gu[:, :f] / (1.0 + np.exp(-gu[:, :f])) * gu[:, f:]
+        return h + self._lin(act.astype(np.float32), self.layer[3], "f32")
+
+    def step(self, layers=None):
+        """One whole decode step (all layers + LM head); returns seconds."""
         t0 = time.perf_counter()
-        for x, v, s in mats:
-            (oc.linear_aq4 if enc == "aq4" else oc.linear_fp8)(x, v, s)
+        h = self.x.copy()
+        for _ in range(self.shape.layers if layers is None else layers):
+            h = self.layer_pass(h)
+            h *= np.float32(1.0 / max(1.0, float(np.abs(h).max())))  # keeps the synthetic residual stream bounded
+        self._lin(self._rms(h, self.gamma), self.head, "bf16")
         return time.perf_counter() - t0
 
-    return one_pass, elems, oc.num_threads()
+
+def reference_config(args, shape, enc, descr, world):
+    """The `config` object both arms print (the driver compares them key by key)."""
+    return {"workload": f"{descr}, batch {args.batch}, tensor-parallel over {world} GPU(s)", "batch": args.batch,
+            "encoding": enc, "layers": shape.layers, "hidden": shape.hidden, "ffn": shape.ffn,
+            "vocab": shape.vocab, "parallelism": f"tp{world}",
+            "l2": "weights streamed per step exceed L2 many times over (no flush needed)",
+            "layers_overridden": bool(args.layers)}
 
 
-def run_reference(args, shape, enc):
-    """The reference project has no CPU (or any) implementation of this path, so the
-    reference arm times this repository's plain-C port of the format spec on the host cores."""
+def run_reference(args, shape, enc, descr):
+    """The reference project has no CPU (or any) implementation of this path, so the reference arm times this
+    repository's plain-C port of the format spec on the host cores: every step executes ALL layers and the LM head
+    (nothing is extrapolated), with every host core, whatever OMP_NUM_THREADS the launcher exported."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    one_pass, elems, threads = cpu_sample(shape, enc, args.batch)
-    reps = max(1, int(np.ceil(1.0 / max(one_pass(), 1e-4))))  # a step = about one second of host work
+    cpu = CpuStack(shape, enc, args.batch)
     for _ in range(args.warmup):
-        one_pass()
-    times = [sum(one_pass() for _ in range(reps)) / reps for _ in range(args.steps)]
+        cpu.step()
+    times = [cpu.step() for _ in range(args.steps)]
     t = sum(times) / len(times)
-    scale = shape.weight_elements() / elems
-    value = args.batch / (t * scale)
-    sample = (f"one decoder layer (QKV, O, gate+up, down; {elems} weight elements) of the same widths, {reps} passes "
-              f"per step ({t * reps:.2f} s), scaled x{scale:.2f} to the whole stack by weight elements")
+    value = args.batch / t
+    sample = (f"whole steps: {shape.layers} layer passes (QKV, O, gate+up, down with their glue) + LM head per step, "
+              f"{args.steps} timed steps of {t:.2f} s on {cpu.threads} threads; the layers share one layer's weight bytes "
+              f"({cpu.layer_elems} elements, streamed from DRAM every pass)")
     line = {
         "impl": "reference", "metric": "linear-stack decode tokens/s", "value": value, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * scale * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload][2] + f", batch {args.batch}", "batch": args.batch,
-                   "encoding": enc, "note": "CPU port of the spec (the reference has no implementation of this path)"},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 accumulate over e4m3 weights and bf16 activations" if enc == "fp8"
+        else "f32 accumulate over 4-bit weights (fp16 group scales) and bf16 activations",
+        "data": "synthetic",
+        "config": reference_config(args, shape, enc, descr, args.gpus),
+        "note": "CPU port of the spec on the host cores (the reference has no implementation of this path); "
+                "the GPU count only names the arm's configuration",
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def tp_check(U, ctx, q, comm, dist, shape, enc, enc_id, rank, world):
+    """Before anything is timed at N > 1: a 2-layer stack of the benchmark's widths (vocabulary cut to 16032 to
+    bound the host work) at the same tensor-parallel degree runs one step with the fused all-reduce and one with
+    ncclAllReduce; rank 0 walks the oracle chain once (plain-C port, all host threads) and checks
+      * every row-parallel sum (O and down of both layers) at the stated tolerance, against the full-K oracle linear
+        applied to the DEVICE's own inputs gathered from the ranks, plus the residual, and
+      * every rank's slice of the logits against the chain's, as rms error relative to the rms of the logits
+        (a chain of bf16 roundings is only reproducible to the 1-ulp level end to end: bound 2 %).
+    The oracle is the checker here, outside every timed region."""
+    import oracle as o
+    import oracle_c as oc
+    chk = U.StackShape(2, shape.hidden, shape.q_heads, shape.kv_heads, shape.head_dim, shape.ffn, 16032)
+    qd, kvd = chk.q_heads * chk.head_dim, chk.kv_heads * chk.head_dim
+    x = o.synth_activations(SEED, 78, 1, chk.hidden)
+    xb = o.f32_to_bf16_bits(x).reshape(1, chk.hidden)
+    got = {}
+    for mode, flags in (("push", 0), ("nccl", U.STACK_FLAG_NCCL_ONLY)):
+        st = U.Stack(ctx, q, chk, enc_id, max_tokens=1, seed=SEED, tp_rank=rank, tp_size=world, comm=comm,
+                     flags=flags | U.STACK_FLAG_KEEP_ACTIVATIONS)
+        for _ in range(2):  # the second step replays the captured graph
+            logits = st.step_host(xb)
+        rec = {"logits": logits}
+        for layer in range(chk.layers):
+            for which, kl, cols in ((U.LINEAR_O, qd // world, (qd + 2 * kvd) // world), (U.LINEAR_DOWN, chk.ffn // world, chk.ffn // world)):
+                info = st.linear_info(layer, which)
+                rec[(layer, which)] = (q.download(info.last_input, (1, cols), np.uint16)[:, :kl].copy(),
+                                       q.download(info.last_residual, (1, chk.hidden), np.float32),
+                                       q.download(info.last_output, (1, chk.hidden), np.float32))
+        _, rec["launches"] = st.stats()
+        st.close()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, rec)
+        got[mode] = gathered
+    result = None
+    if rank == 0:
+        oc.set_num_threads(os.cpu_count() or 1)
+
+        def weight(layer, which, n, k):
+            w = oc.synth_weights(SEED, o.stack_tensor_id(layer, which), n, k)
+            return oc.aq4_quantize(w) if enc == "aq4" else oc.fp8_quantize(w)
+
+        def lin(x_f32, w, want):
+            bits = o.f32_to_bf16_bits(np.ascontiguousarray(x_f32, np.float32)).reshape(x_f32.shape)
+            return (oc.linear_aq4 if enc == "aq4" else oc.linear_fp8)(bits, w[0], w[1], want=want)
+
+        worst = {m: {"max_rel_floored": 0.0, "mean_abs": 0.0} for m in got}
+        h = x.astype(np.float32)
+        for layer in range(chk.layers):
+            g1, g2 = o.stack_gamma(SEED, layer, o.STACK_QKV, chk.hidden), o.stack_gamma(SEED, layer, o.STACK_GATE_UP, chk.hidden)
+            qkv = lin(o.rmsnorm(o.bf16_round(h), 1e-5, g1), weight(layer, o.STACK_QKV, qd + 2 * kvd, chk.hidden), "bf16")
+            wo = weight(layer, o.STACK_O, chk.hidden, qd)
+            h1 = (h + lin(qkv[:, :qd], wo, "f32")).astype(np.float32)
+            gu = o.swiglu(lin(o.rmsnorm(o.bf16_round(h1), 1e-5, g2), weight(layer, o.STACK_GATE_UP, 2 * chk.ffn, chk.hidden), "bf16"))
+            wd = weight(layer, o.STACK_DOWN, chk.hidden, chk.ffn)
+            h = (h1 + lin(gu, wd, "f32")).astype(np.float32)
+            for mode, ranks in got.items():
+                for which, w in ((U.LINEAR_O, wo), (U.LINEAR_DOWN, wd)):
+                    xin = o.bf16_bits_to_f32(np.concatenate([r[(layer, which)][0] for r in ranks], axis=1))
+                    resid, out = ranks[0][(layer, which)][1], ranks[0][(layer, which)][2]
+                    stt = o.error_stats(out, (resid + lin(xin, w, "f32")).astype(np.float32))
+                    for key in worst[mode]:
+                        worst[mode][key] = max(worst[mode][key], stt[key] if stt["nan"] == 0 and stt["inf"] == 0 else float("inf"))
+        ref = lin(o.rmsnorm(o.bf16_round(h), 1e-5, o.stack_gamma(SEED, 0, o.STACK_LM_HEAD, chk.hidden)),
+                  weight(0, o.STACK_LM_HEAD, chk.vocab, chk.hidden), "bf16")
+        result = {"stack": "2 layers of the benchmark's widths, vocabulary 16032, 1 token", "modes": {}}
+        ok = True
+        for mode, ranks in got.items():
+            dev = np.concatenate([o.bf16_bits_to_f32(r["logits"]) for r in ranks], axis=1)
+            rel = float(np.sqrt(np.mean((dev - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)))
+            fine = bool(np.isfinite(dev).all() and rel < 0.02 and worst[mode]["max_rel_floored"] <= 1e-2
+                        and worst[mode]["mean_abs"] <= 1e-3)
+            result["modes"][mode] = {"max_rel_floored": worst[mode]["max_rel_floored"], "mean_abs": worst[mode]["mean_abs"],
+                                     "logits_rel_rms": rel, "launches_per_step": ranks[0]["launches"], "pass": fine}
+            ok = ok and fine
+        result.update({"mode": "push+nccl", "max_rel_floored": max(v["max_rel_floored"] for v in result["modes"].values()),
+                       "mean_abs": max(v["mean_abs"] for v in result["modes"].values()), "pass": ok})
+    box = [result]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
+def time_stack(stack, q, B, xin, yout, steps, warmup):
+    """Device time per step (ms) of `steps` steps after `warmup`, between two events on the stack's queue."""
+    for _ in range(warmup):
+        stack.step(B, xin.at(0), yout.at(0))
+    q.synchronize()
+    a = q.signal()
+    for _ in range(steps):
+        stack.step(B, xin.at(0), yout.at(0))
+    b = q.signal()
+    b.query(3600000)
+    ms = b.elapsed_ms_since(a) / steps
+    a.close()
+    b.close()
+    return ms
 
 
 def time_matvec_extra(U, ctx, q, enc_id, n, k, m, reps, kernel=None):
@@ -216,7 +375,7 @@ def tensor_peaks():
         with open(path) as f:
             p = json.load(f)
         return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured (MEASURED_PEAKS.json)"
-    return 1590.0, 1400.0, "fallback (1.59 PFLOP/s burst, earlier measurement on this pool)"
+    return 1590.0, 1400.0, "fallback (1.59 PFLOP/s cuBLAS bf16 burst figure; MEASURED_PEAKS.json absent)"
 
 
 def time_gemm(U, ctx, q, enc_id, m, n, k, reps):
@@ -308,6 +467,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; the line says so)")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-matvec figures and the CPU baseline")
     ap.add_argument("--nccl-only", action="store_true", help="sum over ranks with ncclAllReduce instead of the fused peer-memory push")
+    ap.add_argument("--gather", default="auto", choices=["auto", "block", "cluster"],
+                    help="fused all-reduce: how the consuming kernels gather the ranks' slots")
+    ap.add_argument("--no-check", action="store_true", help="skip the tensor-parallel parity check that precedes the timed region")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -324,7 +486,7 @@ def main():
     if args.layers:
         shape = U.StackShape(args.layers, shape.hidden, shape.q_heads, shape.kv_heads, shape.head_dim, shape.ffn, shape.vocab)
     if args.impl == "reference":
-        run_reference(args, shape, enc)
+        run_reference(args, shape, enc, descr)
         return
     enc_id = U.ENCODING_AQ4 if enc == "aq4" else U.ENCODING_FP8_CHANNEL
 
@@ -350,8 +512,19 @@ def main():
         comm = U.Comm(ctx, box[0], rank, world)
 
     B = args.batch
-    stack = U.Stack(ctx, q, shape, enc_id, max_tokens=B, seed=SEED, tp_rank=rank, tp_size=world, comm=comm,
-                    flags=U.STACK_FLAG_NCCL_ONLY if args.nccl_only else 0)
+    check = None
+    if world > 1 and not args.no_check:
+        check = tp_check(U, ctx, q, comm, dist, shape, enc, enc_id, rank, world)
+        if not check["pass"]:
+            if rank == 0:
+                print(json.dumps({"check": check, "error": "tensor-parallel results differ from the oracle"}), flush=True)
+            raise SystemExit(3)
+    extras_on = rank == 0 and world == 1 and not args.no_extra
+    flags = (U.STACK_FLAG_NCCL_ONLY if args.nccl_only else 0) | {"auto": 0, "block": U.STACK_FLAG_GATHER_PER_BLOCK,
+                                                                  "cluster": U.STACK_FLAG_GATHER_PER_CLUSTER}[args.gather]
+    # at N = 1 the same stack also serves the batch-32 figure of the extra block
+    stack = U.Stack(ctx, q, shape, enc_id, max_tokens=max(B, 32) if extras_on and args.workload == "stack70b-fp8" else B,
+                    seed=SEED, tp_rank=rank, tp_size=world, comm=comm, flags=flags)
     xin = ctx.alloc(B * shape.hidden * 2)
     yout = ctx.alloc(B * stack.local_vocab * 2)
     q.synth_activations(SEED, 77, 0, B * shape.hidden, xin.at(0))
@@ -419,28 +592,47 @@ def main():
             "dtype": "f32 accumulate over e4m3 weights and bf16 activations" if enc == "fp8"
             else "f32 accumulate over 4-bit weights (fp16 group scales) and bf16 activations",
             "data": "synthetic",
-            "config": {"workload": f"{descr}, batch {B}, tensor-parallel over {world} GPU(s)", "batch": B,
-                       "encoding": enc, "layers": shape.layers, "hidden": shape.hidden, "ffn": shape.ffn,
-                       "vocab": shape.vocab, "parallelism": f"tp{world}",
-                       "l2": "weights streamed per step exceed L2 many times over (no flush needed)",
-                       "layers_overridden": bool(args.layers)},
+            "config": reference_config(args, shape, enc, descr, world),
+            "check": check,
             "e2e": {"value": B * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": B * shape.hidden * 2,
                     "d2h_bytes_per_step": B * stack.local_vocab * 2, "ms_per_step": e2e_s / args.steps * 1e3},
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
+                         "traffic": stack_traffic(enc, world, w_algo + a_algo), "peak_source": peak_src,
+                         "traffic_source": TRAFFIC_NOTE,
                          "kernel": f"matvec_kernel ({n_matvec} launches per step"
                                    + (f" + {2 * shape.layers} all-reduces" if world > 1 else "") + ")",
                          "algorithmic_bytes_per_step": w_algo + a_algo,
                          "note": "achieved = per-GPU algorithmic bytes of one step / device time of one step"},
         }
 
-    # ---- explanatory figures (rank 0, N = 1 only): single matvec shapes and the CPU port ----------
+    # ---- explanatory figures (rank 0, N = 1 only): the other benchmark configurations, single shapes, the CPU port
+    stacks = {}
+    if extras_on and args.workload == "stack70b-fp8":
+        x32, y32 = ctx.alloc(32 * shape.hidden * 2), ctx.alloc(32 * stack.local_vocab * 2)
+        q.synth_activations(SEED, 79, 0, 32 * shape.hidden, x32.at(0))
+        ms = time_stack(stack, q, 32, x32, y32, 10, 3)
+        stacks["stack70b_fp8_batch32"] = {"ms_per_step": ms, "tokens_per_s": 32 / (ms * 1e-3)}
+        x32.close()
+        y32.close()
     stack.close()
     xin.close()
     yout.close()
-    if rank == 0 and world == 1 and not args.no_extra:
+    if extras_on:
+        if args.workload == "stack70b-fp8":
+            s8 = U.Stack(ctx, q, U.LLAMA3_8B, U.ENCODING_AQ4, max_tokens=64, seed=SEED)
+            x8, y8 = ctx.alloc(64 * 4096 * 2), ctx.alloc(64 * s8.local_vocab * 2)
+            q.synth_activations(SEED, 80, 0, 64 * 4096, x8.at(0))
+            w8, _ = s8.stats()
+            for b8 in (1, 16, 64):
+                ms = time_stack(s8, q, b8, x8, y8, 20, 3)
+                stacks[f"stack8b_aq4_batch{b8}"] = {"ms_per_step": ms, "tokens_per_s": b8 / (ms * 1e-3),
+                                                    "weight_gbs": w8 / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": w8 / (ms * 1e-3) / 1e9 / peak}
+            s8.close()
+            x8.close()
+            y8.close()
+        line["stacks"] = stacks
         extra = {}
         for name, e, n, k, m in (("aq4_m1_k4096_n4096", U.ENCODING_AQ4, 4096, 4096, 1),
                                  ("fp8_m1_k4096_n14336", U.ENCODING_FP8_CHANNEL, 14336, 4096, 1),
@@ -461,19 +653,30 @@ def main():
             r["frac_of_peak"] = r["tflops"] / burst
             gemms[name] = r
         line["gemm"] = gemms
-        one_pass, elems, threads = cpu_sample(shape, enc, B)
-        one_pass()
+        # the CPU port beside it: a bounded sample (about twelve seconds) of the same step with every host core, and
+        # one decoder layer on a single core
+        cpu = CpuStack(shape, enc, B)
+        h = cpu.x.copy()
+        cpu.layer_pass(h)
         passes, spent = [], 0.0
-        while spent < 12.0 and len(passes) < 2000:  # about twelve seconds of host work
-            passes.append(one_pass())
+        while spent < 12.0 and len(passes) < 4000:
+            t0 = time.perf_counter()
+            cpu.layer_pass(h)
+            passes.append(time.perf_counter() - t0)
             spent += passes[-1]
         t = sum(passes) / len(passes)
-        scale = shape.weight_elements() / elems
+        scale = shape.weight_elements() / cpu.layer_elems
+        cpu.oc.set_num_threads(1)
+        t0 = time.perf_counter()
+        cpu.layer_pass(h)
+        t1 = time.perf_counter() - t0
         line["cpu_baseline"] = {
-            "value": B / (t * scale), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"one decoder layer of the same widths ({elems} weight elements), {len(passes)} passes in "
-                      f"{spent:.1f} s with {threads} threads (mean {t * 1e3:.1f} ms), scaled x{scale:.1f} to the whole "
-                      f"stack by weight elements"}
+            "value": B / (t * scale), "unit": "tokens/s", "cores": cpu.threads, "kind": "port",
+            "single_thread_value": B / (t1 * scale),
+            "sample": f"one decoder layer of the same widths with its glue ({cpu.layer_elems} weight elements), {len(passes)} "
+                      f"passes in {spent:.1f} s with {cpu.threads} threads (mean {t * 1e3:.1f} ms; one pass on a single thread "
+                      f"{t1 * 1e3:.0f} ms), scaled x{scale:.1f} to the whole stack by weight elements; the reference arm "
+                      f"(--impl reference) executes whole steps instead"}
     elif rank == 0:
         line["cpu_baseline"] = None
     if comm is not None:

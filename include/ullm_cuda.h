@@ -14,8 +14,11 @@
  *   - host data is copied during the call; the library keeps no pointer into
  *     caller memory after return (native/hip/src/hip_evidence_runtime.hip.cpp:618-620);
  *   - completion = submit -> wait(timeout_ms) -> destroy; wait polls, it never
- *     blocks without a deadline; a completion is consumed by wait
- *     (native/hip/src/evidence_abi.h:48-59, hip_evidence_runtime.hip.cpp:508-535, :691-698);
+ *     blocks without a deadline; a completion is consumed by wait, whatever the outcome
+ *     (native/hip/src/evidence_abi.h:48-59, hip_evidence_runtime.hip.cpp:508-535, :691-716);
+ *   - no destructor blocks on the device: what may still be in use is retired in the
+ *     background once its completion is proven, and never freed before that
+ *     (hip_evidence_runtime.hip.cpp:77-103, :151-257);
  *   - there is no CPU fallback: without a usable sm_100 device every compute
  *     entry returns ULLM_STATUS_CUDA_UNAVAILABLE
  *     (native/hip/src/hip_evidence_stub.cpp:103-127).
@@ -168,12 +171,24 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_context_probe(const ullm_cuda_context_t *c
  * :585-659 with objects that are created once and reused. ---------------------- */
 ULLM_CUDA_API ullm_status_t ullm_cuda_context_create(uint32_t device_ordinal, ullm_cuda_context_t **context,
                                        ullm_cuda_error_sink_t *error_sink);
+/* Fails with ULLM_STATUS_INVALID_ARGUMENT while the context still owns queues, buffers, graphs, comms or
+ * stacks; an object destroyed while its queue was busy counts as owned until its background retirement ends. */
 ULLM_CUDA_API ullm_status_t ullm_cuda_context_destroy(ullm_cuda_context_t **context, ullm_cuda_error_sink_t *error_sink);
+/* Limit of every device-side wait of kernels launched for this context afterwards (the fused all-reduce's
+ * wait for a peer's partial sums, the GEMM's pipeline barriers): 1 .. 600000 ms, default 20000.  A wait that
+ * runs out makes its kernel return; everything queued behind it on the context returns without waiting, and
+ * the next ullm_cuda_completion_wait reports ULLM_STATUS_CUDA_DEVICE_FLAGGED (results are not valid). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_context_set_wait_limit(ullm_cuda_context_t *context, uint32_t limit_ms,
+                                               ullm_cuda_error_sink_t *error_sink);
 ULLM_CUDA_API ullm_status_t ullm_cuda_queue_create(ullm_cuda_context_t *context, ullm_cuda_queue_t **queue,
                                      ullm_cuda_error_sink_t *error_sink);
+/* Returns at once.  The stream and the queue's staging memory are released when the queue's last work is
+ * observed complete (immediately if it already is); the handle is dead either way. */
 ULLM_CUDA_API ullm_status_t ullm_cuda_queue_destroy(ullm_cuda_queue_t **queue, ullm_cuda_error_sink_t *error_sink);
 ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_alloc(ullm_cuda_context_t *context, uint64_t size_bytes,
                                      ullm_cuda_buffer_t **buffer, ullm_cuda_error_sink_t *error_sink);
+/* Returns at once.  The memory is freed when every queue of the context that was busy at the time of the
+ * call has finished the work it had then (immediately if all were idle). */
 ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_free(ullm_cuda_buffer_t **buffer, ullm_cuda_error_sink_t *error_sink);
 ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_size(const ullm_cuda_buffer_t *buffer, uint64_t *size_bytes,
                                     ullm_cuda_error_sink_t *error_sink);
@@ -185,8 +200,9 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_download(ullm_cuda_queue_t *queue, 
                                         uint64_t size_bytes, ullm_cuda_error_sink_t *error_sink);
 ULLM_CUDA_API ullm_status_t ullm_cuda_buffer_fill(ullm_cuda_queue_t *queue, ullm_cuda_tensor_t dst, uint8_t value,
                                     uint64_t size_bytes, ullm_cuda_error_sink_t *error_sink);
-/* Records a completion point on the queue (an event with timing).  The handle
- * is consumed by ullm_cuda_completion_wait unless that call times out. */
+/* Records a completion point on the queue (an event with timing).  The handle is consumed by
+ * ullm_cuda_completion_wait.  Refused with ULLM_STATUS_CUDA_RUNTIME_ERROR while too many destroyed objects
+ * still wait for proof that the device has finished with them (at most 8), or after one such proof failed. */
 ULLM_CUDA_API ullm_status_t ullm_cuda_queue_signal(ullm_cuda_queue_t *queue, ullm_cuda_completion_t **completion,
                                      ullm_cuda_error_sink_t *error_sink);
 
@@ -203,14 +219,15 @@ typedef struct ullm_cuda_completion_result_t { /* evidence_abi.h:27-40 */
 } ullm_cuda_completion_result_t;
 
 /* timeout_ms == 0 is a single poll (hip_evidence_runtime.hip.cpp:508-535).
- * On ULLM_STATUS_CUDA_TIMEOUT the handle stays valid; on every other outcome it
- * is consumed and a later use returns ULLM_STATUS_CUDA_INVALID_HANDLE. result may be NULL. */
+ * The handle is consumed by EVERY outcome, ULLM_STATUS_CUDA_TIMEOUT included (hip_evidence_runtime.hip.cpp:691-716:
+ * "a caller cannot retry"); a later use returns ULLM_STATUS_CUDA_INVALID_HANDLE.  To poll without consuming,
+ * use ullm_cuda_completion_query.  result may be NULL. */
 ULLM_CUDA_API ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint32_t timeout_ms,
                                         ullm_cuda_completion_result_t *result,
                                         ullm_cuda_error_sink_t *error_sink);
 /* Milliseconds of device time between two completions that have both been
- * reached (the handles stay valid: use this BEFORE waiting consumes them, or
- * wait with a timeout that keeps them — see ullm_cuda_completion_query). */
+ * reached (the handles stay valid: use this BEFORE a wait consumes them; ullm_cuda_completion_query tells
+ * when they have been reached). */
 ULLM_CUDA_API ullm_status_t ullm_cuda_completion_elapsed_ms(ullm_cuda_completion_t *start, ullm_cuda_completion_t *end,
                                               float *milliseconds, ullm_cuda_error_sink_t *error_sink);
 /* Poll without consuming: OK when reached, ULLM_STATUS_CUDA_TIMEOUT when not. */
@@ -257,7 +274,7 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_dequantize(ullm_cuda_queue_t *queue, const
 
 /* ---- the linear op: y[M,N] = prologue(x)[M,K] . W'[N,K]^T, fp32 accumulate ------ */
 #define ULLM_CUDA_PROLOGUE_NONE UINT32_C(0)
-#define ULLM_CUDA_PROLOGUE_RMSNORM UINT32_C(1) /* x <- bf16(x * rsqrt(mean(x^2) + eps)), weight-free */
+#define ULLM_CUDA_PROLOGUE_RMSNORM UINT32_C(1) /* x <- bf16(x * rsqrt(mean(x^2) + eps) * gamma); gamma = 1 without norm_weight */
 #define ULLM_CUDA_PROLOGUE_SWIGLU UINT32_C(2)  /* input is [M,2K] (gate | up); x <- bf16(silu(gate) * up) */
 
 #define ULLM_CUDA_EPILOGUE_NONE UINT32_C(0)
@@ -284,14 +301,22 @@ typedef struct ullm_cuda_linear_desc_t {
   uint32_t kernel;
   float rms_eps;
   uint32_t epilogue;
+  ullm_cuda_tensor_t norm_weight; /* RMSNorm prologue: gamma, bf16 [K]; buffer NULL = no weight vector */
+  ullm_cuda_tensor_t residual;    /* f32 [M, N] added to the fp32 result before the output conversion
+                                     (y = x . W'^T + residual; may alias the output); buffer NULL = none.
+                                     Not offered together with the SwiGLU epilogue. */
+  uint64_t residual_row_stride;   /* elements; 0 = dense (N) */
   uint32_t reserved[4];
 } ullm_cuda_linear_desc_t;
 
-/* Answers without touching the device: OK, UNSUPPORTED (with a reason in the
- * sink) or an argument error.  Mirrors Backend::supports (crates/ullm-core/src/backend.rs:8). */
+/* Answers from the descriptor's shapes, dtypes and encoding alone: no handle is resolved and neither the
+ * driver nor a device is touched.  OK, UNSUPPORTED (with a reason in the sink) or an argument error.
+ * Mirrors Backend::supports (crates/ullm-core/src/backend.rs:8). */
 ULLM_CUDA_API ullm_status_t ullm_cuda_linear_supports(const ullm_cuda_linear_desc_t *desc, uint32_t *selected_kernel,
                                         ullm_cuda_error_sink_t *error_sink);
-/* Enqueue only (ordering by the queue; use ullm_cuda_queue_signal to observe completion). */
+/* Enqueue only (ordering by the queue; use ullm_cuda_queue_signal to observe completion).
+ * Tensor-core (GEMM) linears stage their activations in scratch memory owned by the QUEUE, so linears on
+ * different queues may overlap freely; the scratch grows on demand (not during a stream capture). */
 ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
                                        ullm_cuda_error_sink_t *error_sink);
 /* Enqueue + signal in one call: the submit -> wait -> destroy shape of evidence_abi.h:48-59. */
@@ -303,9 +328,10 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, co
  * (GEMM) kernel, for callers that must not trigger a device allocation: a serving loop that has
  * handed all free HBM to its own pool (so cudaMalloc would fail or fragment it), or a thread that
  * cannot afford the implicit device-wide synchronisation an allocation or a free may cause.
- * The GEMM path stages prologue(x) as bf16 before the tensor cores read it; here that staging
- * area is a fixed ULLM_CUDA_STATIC_SCRATCH_BYTES array compiled into the library (every GPU that
- * loads the library carries it until the process exits) instead of the context's growable scratch.
+ * The GEMM path stages prologue(x) as two 8-bit planes plus one scale per token (M * K * 2 bytes and a
+ * little more) before the tensor cores read it; here that staging area is a fixed
+ * ULLM_CUDA_STATIC_SCRATCH_BYTES array compiled into the library (every GPU that loads the library
+ * carries it until the process exits) instead of the queue's growable scratch.
  *   - M * K * 2 bytes must fit ULLM_CUDA_STATIC_SCRATCH_BYTES, else ULLM_STATUS_UNSUPPORTED;
  *     the SwiGLU epilogue is not offered here (ULLM_STATUS_UNSUPPORTED).
  *   - The first call on each device looks the array's device address up once; make that first
@@ -319,9 +345,42 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_qu
                                                                     const ullm_cuda_linear_desc_t *desc,
                                                                     ullm_cuda_error_sink_t *error_sink);
 
+/* ---- the two halves of the fused all-reduce, as single ops --------------------------------------
+ * No counterpart in the reference (it has no multi-GPU code).  The tensor-parallel stack below sums the partial
+ * results of a row-parallel linear WITHOUT a collective kernel: the row-parallel linear stores every fp32
+ * partial result together with a tag as one 8-byte {value, tag} pair into a slot per rank, and the linear that
+ * follows adds the ranks' slots (plus an optional residual) while it stages its input, waiting — with the
+ * context's wait limit — for any pair whose tag is not the expected one yet.  These two entries run the very
+ * same kernels on slots inside an ordinary buffer of ONE device, so that a host can drive its own schedule
+ * and so that the path can be checked without several GPUs (fill the slots of all "ranks" one launch after
+ * the other, then gather).  Both serve 1 <= M <= 8 on the CUDA-core kernel only. */
+typedef struct ullm_cuda_slots_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  ullm_cuda_tensor_t slots;   /* [ranks] slots of M * cols pairs {f32 value, u32 tag}, 16-byte aligned */
+  uint64_t rank_stride_bytes; /* distance between two ranks' slots, a multiple of 16, >= M * cols * 8 */
+  uint32_t ranks;             /* 1 .. 8 */
+  uint32_t rank;              /* partial: the slot this launch fills; reduced: ignored */
+  uint32_t tag;               /* written / expected with every value; any value, but a fresh one per use of the slots */
+  uint32_t gather;            /* reduced: 0 = every thread block reads all slots, 1 = once per thread-block cluster */
+  uint32_t reserved[4];
+} ullm_cuda_slots_t;
+/* y is not written: the fp32 results go to slot `rank` (cols = N).  No prologue restriction; no epilogue, no residual. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue_partial(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                               const ullm_cuda_slots_t *slots, ullm_cuda_error_sink_t *error_sink);
+/* x is not read: the input row m is bf16(desc->residual[m] + sum over ranks of slot[r][m]) (cols = K; here
+ * desc->residual is [M, K] and belongs to the INPUT), then the prologue (NONE or RMSNORM), then the linear.
+ * reduced_out, if its buffer is not NULL, receives the fp32 rows residual + sum (f32 [M, K], dense). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue_reduced(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                               const ullm_cuda_slots_t *slots, ullm_cuda_tensor_t reduced_out,
+                                               ullm_cuda_error_sink_t *error_sink);
+
 /* ---- tensor-parallel communicator (NCCL, loaded at run time) ------------------- */
 #define ULLM_CUDA_COMM_ID_BYTES 128
 ULLM_CUDA_API ullm_status_t ullm_cuda_comm_unique_id(uint8_t id[ULLM_CUDA_COMM_ID_BYTES], ullm_cuda_error_sink_t *error_sink);
+/* size up to 64 ranks; the fused all-reduce of the stack's decode path maps peer memory for up to 8 ranks of
+ * one node and falls back to ncclAllReduce beyond that.  One stack at a time may use a communicator's peer
+ * memory: a second live stack on the same communicator sums with ncclAllReduce. */
 ULLM_CUDA_API ullm_status_t ullm_cuda_comm_create(ullm_cuda_context_t *context, const uint8_t id[ULLM_CUDA_COMM_ID_BYTES],
                                     uint32_t rank, uint32_t size, ullm_cuda_comm_t **comm,
                                     ullm_cuda_error_sink_t *error_sink);
@@ -331,7 +390,13 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_comm_all_reduce(ullm_cuda_comm_t *comm, ul
                                         ullm_cuda_error_sink_t *error_sink);
 ULLM_CUDA_API ullm_status_t ullm_cuda_comm_destroy(ullm_cuda_comm_t **comm, ullm_cuda_error_sink_t *error_sink);
 
-/* ---- linear stack of a decoder: per layer QKV, O, gate+up, down; then the LM head.
+/* ---- linear stack of a decoder: per layer QKV, O, gate+up, down; then the LM head, with the glue of a
+ * decoder block around them (no attention is computed):
+ *     h   = f32(input)
+ *     qkv = QKV(rmsnorm(bf16 h, g1));   h += O(qkv[:, :q]);
+ *     act = swiglu(GateUp(rmsnorm(bf16 h, g2)));   h += Down(act);     per layer
+ *     logits = LMHead(rmsnorm(bf16 h, gf))
+ * The residual stream h is fp32; the RMSNorm weight vectors are bf16(1 + z/8) from the seed.
  * Weights are generated on the device from the seed and quantised in place.
  * tp_size > 1: QKV, gate+up and the LM head are column-parallel (this rank holds
  * its slice of N), O and down are row-parallel (this rank holds its slice of K)
@@ -359,6 +424,11 @@ typedef struct ullm_cuda_stack_desc_t {
 #define ULLM_CUDA_STACK_FLAG_NO_GRAPH UINT32_C(1) /* launch kernels directly instead of replaying a graph */
 #define ULLM_CUDA_STACK_FLAG_KEEP_ACTIVATIONS UINT32_C(2) /* one activation set per layer, readable after a step */
 #define ULLM_CUDA_STACK_FLAG_NCCL_ONLY UINT32_C(4) /* sum over ranks with ncclAllReduce even for decode steps */
+/* How the kernel that follows a row-parallel linear gathers the ranks' partial sums (fused all-reduce, decode):
+ * by default every thread block reads all ranks' slots up to 2 ranks, and from 4 ranks on the blocks of a
+ * thread-block cluster share one reading through distributed shared memory.  These two flags force one way. */
+#define ULLM_CUDA_STACK_FLAG_GATHER_PER_BLOCK UINT32_C(8)
+#define ULLM_CUDA_STACK_FLAG_GATHER_PER_CLUSTER UINT32_C(16)
 
 ULLM_CUDA_API ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_queue_t *queue,
                                      ullm_cuda_comm_t *comm, const ullm_cuda_stack_desc_t *desc,
@@ -389,11 +459,14 @@ typedef struct ullm_cuda_stack_linear_info_t {
   uint64_t row_begin; /* shard origin inside the full weight */
   uint64_t col_begin;
   ullm_cuda_tensor_t last_input;  /* activation span this linear read in the last step */
-  ullm_cuda_tensor_t last_output; /* and the span it wrote */
+  ullm_cuda_tensor_t last_output; /* and the span it wrote (row-parallel linears: residual + sum over ranks) */
   uint32_t input_dtype;
   uint32_t output_dtype;
   uint32_t prologue;
   uint32_t epilogue;
+  ullm_cuda_tensor_t norm_weight;   /* gamma of the RMSNorm prologue, bf16 [K]; buffer NULL when there is none */
+  ullm_cuda_tensor_t last_residual; /* f32 [m, N] added to the result in the last step; buffer NULL when none */
+  uint64_t norm_tensor_id;          /* stream id of gamma */
   uint32_t reserved[4];
 } ullm_cuda_stack_linear_info_t;
 
@@ -422,14 +495,17 @@ static_assert(sizeof(ullm_cuda_context_probe_result_t) == 32U, "context probe AB
 static_assert(sizeof(ullm_cuda_tensor_t) == 16U, "tensor span ABI layout changed");
 static_assert(sizeof(ullm_cuda_weight_t) == 56U, "weight ABI layout changed");
 static_assert(sizeof(ullm_cuda_completion_result_t) == 56U, "completion result ABI layout changed");
-static_assert(sizeof(ullm_cuda_linear_desc_t) == 160U, "linear descriptor ABI layout changed");
+static_assert(sizeof(ullm_cuda_linear_desc_t) == 200U, "linear descriptor ABI layout changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, norm_weight) == 144U, "linear norm_weight offset changed");
+static_assert(offsetof(ullm_cuda_linear_desc_t, residual) == 160U, "linear residual offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, weight) == 8U, "linear weight offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, m) == 64U, "linear m offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, input) == 72U, "linear input offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, output) == 96U, "linear output offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, input_dtype) == 120U, "linear input_dtype offset changed");
+static_assert(sizeof(ullm_cuda_slots_t) == 64U, "slots descriptor ABI layout changed");
 static_assert(sizeof(ullm_cuda_stack_desc_t) == 88U, "stack descriptor ABI layout changed");
-static_assert(sizeof(ullm_cuda_stack_linear_info_t) == 168U, "stack linear info ABI layout changed");
+static_assert(sizeof(ullm_cuda_stack_linear_info_t) == 208U, "stack linear info ABI layout changed");
 #endif
 
 #endif /* ULLM_CUDA_H */

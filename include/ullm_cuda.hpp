@@ -190,19 +190,29 @@ struct CompletionReport {
 class Completion {
  public:
   explicit Completion(ullm_cuda_completion_t *c) : h_(c) {}
-  // Waits up to `timeout`.  nullopt = not reached yet, the completion stays usable; otherwise the handle is
-  // consumed.  The timeout saturates at u32::MAX milliseconds and a sub-millisecond one is a single poll
-  // (lib.rs:400-402).
+  // Waits up to `timeout` and CONSUMES the completion whatever the outcome, like the reference's
+  // Completion::wait(self, ..) (crates/ullm-hip/src/lib.rs:404-441): nullopt = not reached before the deadline
+  // (the library has retired the handle; nothing can be retried on it).  The timeout saturates at u32::MAX
+  // milliseconds and a sub-millisecond one is a single poll (lib.rs:400-402).  To poll without consuming use
+  // reached().
   std::optional<CompletionReport> wait(std::chrono::nanoseconds timeout) {
     const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(timeout).count();
     const uint32_t t = ms <= 0 ? 0u : ms > (long long)std::numeric_limits<uint32_t>::max() ? std::numeric_limits<uint32_t>::max() : (uint32_t)ms;
     detail::Sink s;
     auto r = detail::make_struct<ullm_cuda_completion_result_t>();
     const uint32_t raw = ullm_cuda_completion_wait(h_.get(), t, &r, s.get());
+    (void)h_.release();  // consumed by the library on every outcome
     if (raw == ULLM_STATUS_CUDA_TIMEOUT) return std::nullopt;
-    (void)h_.release();  // consumed by the library on every other outcome
     detail::check(raw, s);
     return CompletionReport{r.dispatch_count, r.copy_count, r.selected_backend, r.fallback_used, r.device_flags};
+  }
+  // Single poll that keeps the completion.
+  bool reached() {
+    detail::Sink s;
+    const uint32_t raw = ullm_cuda_completion_query(h_.get(), 0, s.get());
+    if (raw == ULLM_STATUS_CUDA_TIMEOUT) return false;
+    detail::check(raw, s);
+    return true;
   }
 
  private:
@@ -246,6 +256,8 @@ struct QuantLinear {
   uint32_t input_dtype = ULLM_CUDA_DTYPE_BF16, output_dtype = ULLM_CUDA_DTYPE_BF16;
   uint32_t prologue = 0, epilogue = ULLM_CUDA_EPILOGUE_NONE, kernel = ULLM_CUDA_KERNEL_AUTO;
   float rms_eps = 1e-5f;
+  ullm_cuda_tensor_t norm_weight{nullptr, 0};  // RMSNorm prologue: bf16 gamma[K]
+  ullm_cuda_tensor_t residual{nullptr, 0};     // f32 [M, N] added to the result
 
   ullm_cuda_linear_desc_t desc() const {
     auto d = detail::make_struct<ullm_cuda_linear_desc_t>();
@@ -264,6 +276,8 @@ struct QuantLinear {
     d.kernel = kernel;
     d.rms_eps = rms_eps;
     d.epilogue = epilogue;
+    d.norm_weight = norm_weight;
+    d.residual = residual;
     return d;
   }
 };

@@ -232,11 +232,15 @@ def linear(x_bf16_as_f32: np.ndarray, w_deq: np.ndarray, out: str = "bf16") -> n
     return bf16_round(y) if out == "bf16" else y
 
 
-def rmsnorm(x: np.ndarray, eps: float = 1e-5) -> np.ndarray:
-    """Weight-free RMSNorm of bf16-valued rows, fp64 inside, bf16 result."""
+def rmsnorm(x: np.ndarray, eps: float = 1e-5, gamma: np.ndarray | None = None) -> np.ndarray:
+    """RMSNorm of bf16-valued rows with an optional bf16-valued weight vector gamma [K]:
+    bf16( x * rsqrt(mean(x^2) + eps) * gamma ), fp64 inside, ONE rounding at the end."""
     x64 = x.astype(np.float64)
     r = 1.0 / np.sqrt((x64 * x64).mean(axis=1, keepdims=True) + eps)
-    return bf16_round((x64 * r).astype(np.float32))
+    y = x64 * r
+    if gamma is not None:
+        y = y * np.asarray(gamma, np.float64)[None, :]
+    return bf16_round(y.astype(np.float32))
 
 
 def swiglu(gate_up: np.ndarray) -> np.ndarray:
@@ -351,6 +355,17 @@ def stack_tensor_id(layer: int, which: int) -> int:
     return (layer << 8) | which | (1 << 40)
 
 
+def stack_norm_tensor_id(layer: int, which: int) -> int:
+    """Random-stream id of the RMSNorm weight vector in front of one column-parallel stack linear."""
+    return (layer << 8) | which | (2 << 40)
+
+
+def stack_gamma(seed, layer, which, k) -> np.ndarray:
+    """gamma[i] = bf16(1 + z_i / 8) as fp32 values, z the counter-based normal stream."""
+    z = synth_normal(seed, stack_norm_tensor_id(layer, which), 0, k)
+    return bf16_round((np.float32(1.0) + z * np.float32(0.125)).astype(np.float32))
+
+
 def stack_weight(seed, layer, which, n, k, encoding: str):
     """Dequantised full weight [n,k] of one stack linear ('aq4' or 'fp8')."""
     w = synth_weights(seed, stack_tensor_id(layer, which), n, k)
@@ -362,19 +377,21 @@ def stack_weight(seed, layer, which, n, k, encoding: str):
 def stack_reference(seed, encoding, layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, x, eps=1e-5,
                     trace=None):
     """One pass of the linear stack on bf16-valued x [m, hidden] -> logits (bf16
-    values) [m, vocab].  Dataflow per layer:
-        qkv = QKV(rmsnorm(h));  o = O(qkv[:, :q_dim]) (fp32);
-        act = swiglu(GateUp(rmsnorm(bf16(o))));  h = Down(act) (fp32)
-    then logits = LMHead(rmsnorm(bf16(h))).  `trace`, if a dict, receives every
-    intermediate under (layer, which)."""
+    values) [m, vocab].  The residual stream h is fp32.  Dataflow per layer:
+        qkv = QKV(rmsnorm(bf16(h), g1));  h = h + O(qkv[:, :q_dim])        (fp32 add)
+        act = swiglu(GateUp(rmsnorm(bf16(h), g2)));  h = h + Down(act)
+    then logits = LMHead(rmsnorm(bf16(h), gf)).  `trace`, if a dict, receives every
+    intermediate under (layer, which) (for O and Down: the new h)."""
     qd, kvd = q_heads * head_dim, kv_heads * head_dim
-    h = x
+    h = x.astype(np.float32)
     for l in range(layers):
-        qkv = linear(rmsnorm(bf16_round(h), eps), stack_weight(seed, l, STACK_QKV, qd + 2 * kvd, hidden, encoding))
-        o_ = linear(qkv[:, :qd], stack_weight(seed, l, STACK_O, hidden, qd, encoding), out="f32")
-        gu = swiglu(linear(rmsnorm(bf16_round(o_), eps), stack_weight(seed, l, STACK_GATE_UP, 2 * ffn, hidden, encoding)))
-        h = linear(gu, stack_weight(seed, l, STACK_DOWN, hidden, ffn, encoding), out="f32")
+        g1, g2 = stack_gamma(seed, l, STACK_QKV, hidden), stack_gamma(seed, l, STACK_GATE_UP, hidden)
+        qkv = linear(rmsnorm(bf16_round(h), eps, g1), stack_weight(seed, l, STACK_QKV, qd + 2 * kvd, hidden, encoding))
+        h1 = (h + linear(qkv[:, :qd], stack_weight(seed, l, STACK_O, hidden, qd, encoding), out="f32")).astype(np.float32)
+        gu = swiglu(linear(rmsnorm(bf16_round(h1), eps, g2), stack_weight(seed, l, STACK_GATE_UP, 2 * ffn, hidden, encoding)))
+        h = (h1 + linear(gu, stack_weight(seed, l, STACK_DOWN, hidden, ffn, encoding), out="f32")).astype(np.float32)
         if trace is not None:
-            trace[(l, STACK_QKV)], trace[(l, STACK_O)] = qkv, o_
+            trace[(l, STACK_QKV)], trace[(l, STACK_O)] = qkv, h1
             trace[(l, STACK_GATE_UP)], trace[(l, STACK_DOWN)] = gu, h
-    return linear(rmsnorm(bf16_round(h), eps), stack_weight(seed, 0, STACK_LM_HEAD, vocab, hidden, encoding))
+    gf = stack_gamma(seed, 0, STACK_LM_HEAD, hidden)
+    return linear(rmsnorm(bf16_round(h), eps, gf), stack_weight(seed, 0, STACK_LM_HEAD, vocab, hidden, encoding))

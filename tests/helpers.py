@@ -57,9 +57,9 @@ def oracle_dequantize(v, s, encoding):
 
 def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_BF16, y_dtype=U.DTYPE_BF16,
                prologue=U.PROLOGUE_NONE, kernel=U.KERNEL_AUTO, x_stride=0, y_stride=0, submit=True,
-               epilogue=U.EPILOGUE_NONE):
-    """x_vals: fp32 array [M, cols] (bf16-representable unless x_dtype is F32).
-    Returns (y as fp32 values [M, N], completion result or None)."""
+               epilogue=U.EPILOGUE_NONE, gamma=None, residual=None):
+    """x_vals: fp32 array [M, cols] (bf16-representable unless x_dtype is F32); gamma: bf16-valued fp32 [K] or
+    None; residual: fp32 [M, N] or None.  Returns (y as fp32 values [M, N], completion result or None)."""
     m, cols = x_vals.shape
     xs = x_stride or cols
     n_out = dw.n // 2 if epilogue == U.EPILOGUE_SWIGLU else dw.n
@@ -72,9 +72,21 @@ def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_
     host[:, :cols] = x_vals
     q.upload(xbuf.at(0), o.f32_to_bf16_bits(host).reshape(m, xs) if x_dtype == U.DTYPE_BF16 else host)
     q.fill(ybuf.at(0), CANARY, m * ys * ye + 256)
+    extra = []
+    gt = rt = None
+    if gamma is not None:
+        gbuf = ctx.alloc(len(gamma) * 2)
+        q.upload(gbuf.at(0), o.f32_to_bf16_bits(np.asarray(gamma, np.float32)))
+        gt = gbuf.at(0)
+        extra.append(gbuf)
+    if residual is not None:
+        rbuf = ctx.alloc(residual.size * 4)
+        q.upload(rbuf.at(0), np.ascontiguousarray(residual, np.float32))
+        rt = rbuf.at(0)
+        extra.append(rbuf)
     d = U.linear_desc(dw.desc, m, xbuf.at(0), ybuf.at(0), input_dtype=x_dtype, output_dtype=y_dtype,
                       prologue=prologue, kernel=kernel, input_row_stride=x_stride, output_row_stride=y_stride,
-                      epilogue=epilogue)
+                      epilogue=epilogue, norm_weight=gt, residual=rt)
     res = None
     if submit:
         res = q.linear_submit(d).wait(60000)
@@ -91,18 +103,21 @@ def run_linear(ctx, q, dw: DeviceWeight, x_vals: np.ndarray, *, x_dtype=U.DTYPE_
     if ys > n_out:  # padding columns of a strided output must be untouched
         pad = raw[: m * ys * ye].reshape(m, ys * ye)[:, n_out * ye:]
         assert (pad == CANARY).all(), "kernel wrote into the row padding"
-    xbuf.close()
-    ybuf.close()
+    for b in [xbuf, ybuf] + extra:
+        b.close()
     return y[:, :n_out].copy(), res
 
 
 def oracle_linear(x_vals, w_deq, prologue=U.PROLOGUE_NONE, x_is_f32=False, out="bf16", eps=1e-5,
-                  epilogue=U.EPILOGUE_NONE):
+                  epilogue=U.EPILOGUE_NONE, gamma=None, residual=None):
     x = o.bf16_round(x_vals.astype(np.float32)) if x_is_f32 else x_vals
     if prologue == U.PROLOGUE_RMSNORM:
-        x = o.rmsnorm(x, eps)
+        x = o.rmsnorm(x, eps, gamma)
     elif prologue == U.PROLOGUE_SWIGLU:
         x = o.swiglu(x)
     if epilogue == U.EPILOGUE_SWIGLU:  # rows [gate | up] -> bf16(silu(bf16 gate) * bf16 up)
         return o.swiglu(o.linear(x, w_deq, out="bf16"))
-    return o.linear(x, w_deq, out=out)
+    if residual is None:
+        return o.linear(x, w_deq, out=out)
+    y = (o.linear(x, w_deq, out="f64") + residual.astype(np.float64)).astype(np.float32)  # added before the output rounding
+    return o.bf16_round(y) if out == "bf16" else y

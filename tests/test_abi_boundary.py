@@ -38,7 +38,7 @@ def test_struct_layouts_match_the_header_pins():
                "ullm_cuda_context_probe_result_t": abi.ContextProbeResult, "ullm_cuda_tensor_t": abi.Tensor,
                "ullm_cuda_weight_t": abi.Weight, "ullm_cuda_completion_result_t": abi.CompletionResult,
                "ullm_cuda_linear_desc_t": abi.LinearDesc, "ullm_cuda_stack_desc_t": abi.StackDesc,
-               "ullm_cuda_stack_linear_info_t": abi.StackLinearInfo}
+               "ullm_cuda_stack_linear_info_t": abi.StackLinearInfo, "ullm_cuda_slots_t": abi.Slots}
     assert set(pins) == set(by_name)
     for name, cls in by_name.items():
         assert C.sizeof(cls) == int(pins[name]) == abi.EXPECTED_SIZES[cls], name
@@ -168,13 +168,22 @@ def _desc(enc=abi.ENCODING_AQ4, n=4096, k=4096, m=1, **kw):
 def test_linear_supports_answers_from_shape_alone():
     """Mirrors Backend::supports (crates/ullm-core/src/backend.rs:8): no device needed."""
     assert U.linear_supports(_desc()) == abi.KERNEL_MATVEC
-    assert U.linear_supports(_desc(abi.ENCODING_FP8_CHANNEL, 14336, 4096, 8)) == abi.KERNEL_MATVEC
+    # the same answers with or without a device or driver: a shape query never asks either
+    assert U.linear_supports(_desc(abi.ENCODING_FP8_CHANNEL, 14336, 4096, 8)) == abi.KERNEL_GEMM
+    assert U.linear_supports(_desc(abi.ENCODING_FP8_CHANNEL, 14336, 4096, 1)) == abi.KERNEL_MATVEC
+    assert U.linear_supports(_desc(abi.ENCODING_AQ4, 14336, 4096, 4)) == abi.KERNEL_MATVEC
+    assert U.linear_supports(_desc(abi.ENCODING_AQ4, 14336, 4096, 2048)) == abi.KERNEL_GEMM
+    assert U.linear_supports(_desc(abi.ENCODING_FP8_CHANNEL, 4096, 4112, 4)) == abi.KERNEL_MATVEC  # K % 128 != 0
     for bad, status in ((_desc(k=4000), U.Status.Unsupported),  # ragged K is rejected, not guessed
                         (_desc(abi.ENCODING_NVFP4), U.Status.Unsupported),
                         (_desc(m=0), U.Status.InvalidArgument),
                         (_desc(input_dtype=abi.DTYPE_U8), U.Status.Unsupported),
                         (_desc(prologue=9), U.Status.InvalidArgument),
-                        (_desc(input_row_stride=100), U.Status.InvalidArgument)):
+                        (_desc(input_row_stride=100), U.Status.InvalidArgument),
+                        (_desc(m=5, input_row_stride=1 << 62), U.Status.OutOfRange),  # a span that would wrap 64 bits
+                        (_desc(m=5, output_row_stride=(1 << 40) + 1), U.Status.OutOfRange),
+                        (_desc(epilogue=abi.EPILOGUE_SWIGLU, residual=abi.Tensor(C.c_void_p(1), 0)), U.Status.Unsupported),
+                        (_desc(norm_weight=abi.Tensor(C.c_void_p(1), 0)), U.Status.InvalidArgument)):
         with pytest.raises(U.CudaError) as e:
             U.linear_supports(bad)
         assert e.value.status is status, e.value

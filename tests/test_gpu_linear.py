@@ -192,3 +192,39 @@ def test_graph_capture_replays_a_linear(gpu):
     for b in (xb, yb):
         b.close()
     dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("m,kernel", [(1, U.KERNEL_MATVEC), (3, U.KERNEL_MATVEC), (8, U.KERNEL_GEMM), (40, U.KERNEL_GEMM),
+                                      (200, U.KERNEL_GEMM)])
+def test_rmsnorm_weight_and_residual(gpu, encoding, m, kernel):
+    """The glue of a decoder block around the linear: RMSNorm with a weight vector in front (one rounding:
+    bf16(x * rsqrt(mean x^2 + eps) * gamma)) and a residual added to the fp32 result, on both kernels.
+    (docs/plans/archive/2026/08/1-10/phase2-h3-g0-model-free-gpu.md:42 lists RMSNorm among the first ops.)"""
+    ctx, q = gpu
+    n, k = 384, 1024
+    w = o.synth_weights(SEED, 2100 + m, n, k)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    wdq = oracle_dequantize(*oracle_quantize(w, encoding), encoding)
+    x = (o.synth_normal(SEED, 2200 + m, 0, m * k).reshape(m, k) * np.float32(3.0)).astype(np.float32)  # fp32 input
+    gamma = o.bf16_round((1.0 + 0.25 * o.synth_normal(SEED, 2300, 0, k)).astype(np.float32))
+    res = (o.synth_normal(SEED, 2400 + m, 0, m * n).reshape(m, n) * np.float32(2.0)).astype(np.float32)
+    for out, ydt in (("f32", U.DTYPE_F32), ("bf16", U.DTYPE_BF16)):
+        y, _ = run_linear(ctx, q, dw, x, x_dtype=U.DTYPE_F32, y_dtype=ydt, prologue=U.PROLOGUE_RMSNORM, kernel=kernel,
+                          gamma=gamma, residual=res)
+        ref = oracle_linear(x, wdq, U.PROLOGUE_RMSNORM, x_is_f32=True, out=out, gamma=gamma, residual=res)
+        check(y, ref, (encoding, m, kernel, out))
+    # the weight vector alone, and the residual alone (in place: the residual aliases the output)
+    y, _ = run_linear(ctx, q, dw, x, x_dtype=U.DTYPE_F32, prologue=U.PROLOGUE_RMSNORM, kernel=kernel, gamma=gamma)
+    check(y, oracle_linear(x, wdq, U.PROLOGUE_RMSNORM, x_is_f32=True, gamma=gamma), "gamma only")
+    xb = o.bf16_round(x)
+    ybuf, xbuf = ctx.alloc(m * n * 4), ctx.alloc(m * k * 2)
+    q.upload(ybuf.at(0), res)
+    q.upload(xbuf.at(0), o.f32_to_bf16_bits(xb).reshape(m, k))
+    q.linear_submit(U.linear_desc(dw.desc, m, xbuf.at(0), ybuf.at(0), output_dtype=U.DTYPE_F32, kernel=kernel,
+                                  residual=ybuf.at(0))).wait(60000)
+    y = q.download(ybuf.at(0), (m, n), np.float32)
+    check(y, oracle_linear(xb, wdq, out="f32", residual=res), "in-place residual")
+    ybuf.close()
+    xbuf.close()
+    dw.close()

@@ -46,8 +46,18 @@ def test_tiny_stack_every_linear_matches_the_oracle(gpu, encoding, name, m, flag
         n_out = n // 2 if info.epilogue == U.EPILOGUE_SWIGLU else n
         yout = _read(q, info.last_output, (m, n_out), info.output_dtype)
         wdq = o.stack_weight(SEED, layer, which, n, k, name)
+        gamma = resid = None
+        if info.norm_weight.buffer:  # the RMSNorm weight vector is the seeded one
+            gamma = o.bf16_bits_to_f32(q.download(info.norm_weight, (k,), np.uint16))
+            assert np.array_equal(gamma, o.stack_gamma(SEED, layer, which, k)), (layer, which)
+            assert info.norm_tensor_id == o.stack_norm_tensor_id(layer, which)
+        if info.last_residual.buffer:  # row-parallel linears: the residual stream they added their result to
+            resid = q.download(info.last_residual, (m, n), np.float32)
+        assert bool(info.norm_weight.buffer) == (which in (U.LINEAR_QKV, U.LINEAR_GATE_UP, U.LINEAR_LM_HEAD))
+        assert bool(info.last_residual.buffer) == (which in (U.LINEAR_O, U.LINEAR_DOWN))
         ref = oracle_linear(xin, wdq, info.prologue, x_is_f32=info.input_dtype == U.DTYPE_F32,
-                            out="f32" if info.output_dtype == U.DTYPE_F32 else "bf16", epilogue=info.epilogue)
+                            out="f32" if info.output_dtype == U.DTYPE_F32 else "bf16", epilogue=info.epilogue,
+                            gamma=gamma, residual=resid)
         stt = o.error_stats(yout, ref)
         if info.epilogue == U.EPILOGUE_SWIGLU:
             # the epilogue works on bf16 gate|up values: a gate that sits on a rounding tie flips by one ulp with
@@ -66,7 +76,7 @@ def test_tiny_stack_every_linear_matches_the_oracle(gpu, encoding, name, m, flag
     assert np.array_equal(q.download(yout.at(0), (m, TINY.vocab), np.uint16), st.step_host(xb))
     wb, launches = st.stats()
     linears = TINY.layers * 4 + 1  # one matvec launch each, or activation planes + GEMM (+ SwiGLU) on the tensor-core path
-    assert linears <= launches <= 3 * linears
+    assert linears + 1 <= launches <= 3 * linears + 1  # + the kernel that starts the residual stream
     per = {U.ENCODING_AQ4: lambda n, k: n * k // 2 + n * k // 64, U.ENCODING_FP8_CHANNEL: lambda n, k: n * k + 4 * n}[encoding]
     want = TINY.layers * (per(qd + 2 * TINY.kv_heads * TINY.head_dim, TINY.hidden) + per(TINY.hidden, qd)
                           + per(2 * TINY.ffn, TINY.hidden) + per(TINY.hidden, TINY.ffn)) + per(TINY.vocab, TINY.hidden)

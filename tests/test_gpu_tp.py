@@ -16,12 +16,13 @@ def _gpus():
     return U.backend_probe().device_count
 
 
-@pytest.mark.parametrize("enc,m,mode", [("fp8", 1, "push"), ("aq4", 4, "push"), ("fp8", 8, "nccl"), ("fp8", 24, "push")])
+@pytest.mark.parametrize("enc,m,mode", [("fp8", 1, "push"), ("aq4", 4, "push"), ("fp8", 8, "nccl"), ("fp8", 24, "push"),
+                                        ("fp8", 1, "push-cluster"), ("aq4", 2, "push-cluster"), ("fp8", 3, "push-block")])
 def test_tensor_parallel_stack(enc, m, mode):
     n = _gpus()
     if n < 2:
         pytest.skip("needs two GPUs")
-    world = 4 if n >= 4 else 2
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)  # every GPU of the box: 2, 4 or 8 ranks
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29581", WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), enc, str(m), mode],
                               env=dict(env, RANK=str(r), LOCAL_RANK=str(r)), stdout=subprocess.PIPE,

@@ -79,6 +79,7 @@ struct Comm {
   uint8_t *sym[kMaxPeers] = {};
   size_t sym_bytes = 0;
   bool p2p = false;
+  bool sym_in_use = false;  // a live stack pushes through the buffer: a second one must not share its slots
 };
 
 Comm *as_comm(const ullm_cuda_comm_t *h) {
@@ -89,12 +90,31 @@ Comm *as_comm(const ullm_cuda_comm_t *h) {
 // maps every peer's allocation (CUDA IPC, peer access over NVLink).  Returns false (and leaves
 // the communicator on NCCL only) when any step is not available.
 bool comm_sym_setup(Comm *c, size_t bytes, std::string *why) {
-  if (c->p2p && c->sym_bytes >= bytes) return true;
-  if (c->sym_bytes != 0 || c->size > (uint32_t)kMaxPeers) {
-    if (why) *why = "symmetric memory already set up with a smaller size";
+  Nccl &n = nccl();
+  if (c->sym_in_use) {  // every rank creates and destroys its stacks in the same order: the same verdict everywhere
+    if (why) *why = "another stack is using the communicator's symmetric memory";
     return false;
   }
-  Nccl &n = nccl();
+  if (c->p2p && c->sym_bytes >= bytes) {
+    // Reuse by a later stack: the slots still hold the previous stack's {value, tag} pairs and step counter.
+    // Every rank zeroes its buffer, and one collective makes sure all have done so before anyone pushes again.
+    uint8_t *tok = nullptr;
+    bool ok = cudaMemset(c->sym[c->rank], 0, c->sym_bytes) == cudaSuccess;
+    ok = cudaMalloc(reinterpret_cast<void **>(&tok), 16 * c->size) == cudaSuccess && ok;
+    if (tok != nullptr) {
+      ok = cudaMemset(tok, 0, 16 * c->size) == cudaSuccess && ok;
+      ok = n.AllGather(tok + 16 * c->rank, tok, 16, kNcclChar, c->comm, nullptr) == 0 && ok;
+      ok = cudaStreamSynchronize(nullptr) == cudaSuccess && ok;
+      (void)cudaFree(tok);
+    }
+    if (!ok) (void)cudaGetLastError();
+    c->sym_in_use = ok;
+    return ok;
+  }
+  if (c->sym_bytes != 0 || c->size > (uint32_t)kMaxPeers) {
+    if (why) *why = "symmetric memory already set up with a smaller size, or more ranks than peer slots";
+    return false;
+  }
   // Every rank walks through the same two all-gathers whatever happens locally, so that no rank
   // is left waiting in a collective and all ranks reach the same verdict.
   uint8_t *local = nullptr;
@@ -150,8 +170,10 @@ bool comm_sym_setup(Comm *c, size_t bytes, std::string *why) {
   }
   c->sym_bytes = bytes;
   c->p2p = true;
+  c->sym_in_use = true;
   return true;
 }
+void comm_sym_release(Comm *c) { c->sym_in_use = false; }
 bool comm_p2p(const Comm *c) { return c->p2p; }
 uint8_t *comm_sym_ptr(const Comm *c, uint32_t peer) { return c->sym[peer]; }
 size_t comm_sym_bytes(const Comm *c) { return c->sym_bytes; }
@@ -270,8 +292,10 @@ ullm_status_t ullm_cuda_comm_destroy(ullm_cuda_comm_t **comm, ullm_cuda_error_si
   if (cm == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "comm handle is not live");
   registry().remove(cm);
   (void)cudaSetDevice(cm->ctx->device);
-  (void)cudaDeviceSynchronize();
-  for (uint32_t r = 0; r < cm->size; ++r) {
+  // Destroying a communicator is collective and NCCL's own teardown waits for its kernels; the peers'
+  // mappings are closed first, which needs every stack that pushed through them to be gone (it is: a stack
+  // counts as a child of the context until its queue's work has been observed complete).
+  for (uint32_t r = 0; r < cm->size && r < (uint32_t)kMaxPeers; ++r) {
     if (cm->sym[r] == nullptr) continue;
     if (r == cm->rank)
       (void)cudaFree(cm->sym[r]);

@@ -13,12 +13,18 @@
 //   * An AQ4 weight q = u - 8 (-8..7) becomes the e4m3 byte sign | |q|, which IS the number
 //     q * 2^-9 (the subnormals and the first binade of e4m3 are one linear ramp): about 1.6 integer
 //     instructions per weight, shared memory to shared memory.
-//   * A bf16 activation has 8 significant bits, e4m3 has 4: x * 2^p = hi + lo with hi the e4m3
-//     rounding of the scaled value and lo the e4m3 rounding of the rest (exact whenever the
-//     scaled |x| >= 2^-2; p is chosen per token so that the row's largest magnitude lands in
-//     [128, 256), so only elements 2^-9 and more below the row maximum lose anything, and then
-//     less than 2^-18 of that maximum).  Two MMAs per k-slice, A . hi and A . lo, add into the
-//     same accumulator: twice the instructions at twice the bf16 rate.
+//   * A bf16 activation has 8 significant bits, e4m3 has 4: x * 2^p = hi + lo, p chosen per token so
+//     that the row's largest magnitude lands in [128, 256).  hi = e4m3(x * 2^p) (round to nearest even)
+//     leaves a signed rest of at most 8 units of the element's last bf16 bit: three significant bits.
+//     Wide tiles store lo = e5m2(rest) and issue the second MMA with an e5m2 B operand (the instruction
+//     takes the two operand formats independently) into the SAME accumulator; narrow tiles (up to 64
+//     tokens), whose two planes form one B operand with separate accumulator columns, store
+//     lo = e4m3(16 * rest) and the epilogue adds hi + lo / 16.  Either way the pair is EXACT for every
+//     element whose scaled magnitude is at least 2^-6 (hi in e4m3's normal range), i.e. within a
+//     factor 2^14 of the row's largest magnitude; smaller elements are off by at most 2^-14 scaled
+//     units, 2^-22 of the row maximum (a row whose largest element is more than 2^14 times the typical
+//     one therefore loses one bit of the typical elements per further factor of two).
+//     Two MMAs per k-slice at twice the bf16 rate.
 //
 // Orientation ("swap AB"): the WEIGHT rows are the 128-row M side of the MMA and the TOKENS are
 // its N side (tile of TT = 16..256 tokens), so the per-channel / per-group scale is a per-LANE
@@ -61,7 +67,6 @@ constexpr uint32_t A_BYTES = BM * BKB;        // e4m3 operand tile
 constexpr uint32_t RAW_BYTES = BM * BKB / 2;  // packed nibble tile
 constexpr int MAX_STAGES = 8, MAX_RAW = 8;
 constexpr uint32_t kFlagGemmWait = 2u;
-constexpr uint64_t kWaitLimitNs = 20ull * 1000ull * 1000ull * 1000ull;
 constexpr uint32_t kMaxCounterTiles = 1024;  // phase-2 tiles: fewer than the SM count
 
 struct GemmParams {
@@ -79,6 +84,10 @@ struct GemmParams {
   float *partial;           // [range][head, tail][row block][TT][128] fp32
   uint32_t *tile_counters;  // one per phase-2 tile, zero between launches
   uint32_t *flags;
+  uint32_t *abort_word;     // device-resident: non-zero once any wait of the context has given up
+  uint64_t wait_ns;         // limit of one barrier wait
+  const float *residual;    // f32 [m, res_stride] added to the result, or null
+  uint64_t res_stride;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -107,18 +116,26 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false = the CTA gives up (this thread timed out, or another one did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *device_flags) {
+// Bounded wait: false = the CTA gives up (this thread timed out, or another one did, or an earlier kernel of
+// the context did: the device-resident abort word makes everything queued behind an expired wait unwind at once).
+struct WaitCtl {
+  volatile uint32_t *abort_flag;  // this CTA
+  uint32_t *device_flags;         // host-visible
+  volatile uint32_t *abort_word;  // the context's, in device memory
+  uint64_t limit_ns;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl &w) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 0x3fu) == 0u) {
-      if (*abort_flag != 0u) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1u;
-        if (device_flags != nullptr) atomicOr(device_flags, kFlagGemmWait);
+      if (*w.abort_flag != 0u) return false;
+      const bool aborted = w.abort_word != nullptr && *w.abort_word != 0u;
+      if (aborted || global_timer_ns() - t0 > w.limit_ns) {
+        *w.abort_flag = 1u;
+        if (w.abort_word != nullptr) atomicOr(const_cast<uint32_t *>(w.abort_word), 1u);
+        if (w.device_flags != nullptr) atomicOr(w.device_flags, kFlagGemmWait);
         return false;
       }
     }
@@ -354,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  const WaitCtl wctl{&abort_flag, p.flags, p.abort_word, p.wait_ns};
   Walker walk(p, tiles_n * tiles_m);
   Segment sg;
 
@@ -368,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
         for (uint32_t i = 0; i < sg.nkb * SUBS; ++i) {
-          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, wctl)) {
             ok = false;
             break;
           }
@@ -392,6 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---- MMA issue ------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_e4m3((int)MMA_N);
+      constexpr uint32_t idesc_lo = idesc | (1u << 10);  // B operand read as e5m2 (the rest plane of wide tiles)
       uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
       while (ok && walk.next(&sg)) {
@@ -399,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ENC == FP8) {
           buf = seg % NB;
           const uint32_t use = seg / NB;
-          if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
+          if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl);
         }
         for (uint32_t i = 0; i < sg.nkb * SUBS && ok; ++i) {
           uint32_t fresh = i == 0 ? 1u : 0u;
@@ -407,10 +426,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             buf = batch % NB;
             const uint32_t use = batch / NB;
             fresh = 1u;
-            if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, &abort_flag, p.flags);
-            ok = ok && mbar_wait(a_full(slot), round & 1u, &abort_flag, p.flags);
+            if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl);
+            ok = ok && mbar_wait(a_full(slot), round & 1u, wctl);
           }
-          ok = ok && mbar_wait(full(slot), round & 1u, &abort_flag, p.flags);
+          ok = ok && mbar_wait(full(slot), round & 1u, wctl);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
@@ -422,7 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
               const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
               tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-              if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc, 1u);
+              if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
             }
           }
           tc_commit(empty(slot));  // the stage may be refilled when these MMAs are done
@@ -452,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
         for (uint32_t i = 0; i < sg.nkb; ++i) {
-          if (round > 0 && !mbar_wait(raw_empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+          if (round > 0 && !mbar_wait(raw_empty(slot), (round - 1) & 1u, wctl)) {
             ok = false;
             break;
           }
@@ -480,7 +499,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       while (ok && walk.next(&sg)) {
         for (uint32_t i = 0; i < sg.nkb; ++i) {
-          if (!mbar_wait(raw_full(rslot), rround & 1u, &abort_flag, p.flags)) {
+          if (!mbar_wait(raw_full(rslot), rround & 1u, wctl)) {
             ok = false;
             break;
           }
@@ -496,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                            : "r"(addr));
             }
           }
-          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, &abort_flag, p.flags)) {
+          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, wctl)) {
             ok = false;
             break;
           }
@@ -572,7 +591,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < CH; ++i) {
           const uint32_t tok = m0 + c + i;
           if (tok < p.m) {
-            const float f = v[i] * (mult * __ldg(p.tok_scale + tok));
+            float f = v[i] * (mult * __ldg(p.tok_scale + tok));
+            if (p.residual != nullptr) f += p.residual[(uint64_t)tok * p.res_stride + row];
             if (p.y_dtype == ULLM_CUDA_DTYPE_F32)
               static_cast<float *>(p.y)[(uint64_t)tok * p.y_stride + row] = f;
             else
@@ -582,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       if (ENC == FP8) {
         const uint32_t buf = seg % NB, use = seg / NB;
-        ok = ok && mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+        ok = ok && mbar_wait(acc_full(buf), use & 1u, wctl);
         if (ok) {
           tc_fence_after();
           if (active) {
@@ -599,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 float f[CH];
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
-                  f[i] = (NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i])) * sc;
+                  f[i] = (NCAT ? fmaf(__uint_as_float(v2[i]), 0.0625f, __uint_as_float(v[i])) : __uint_as_float(v[i])) * sc;
                 emit(r, col0 + c, f, direct);
               }
             }
@@ -624,7 +644,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t buf = batch % NB, use = batch / NB;
             const float sc = sc_next;
             if (g + 1 < sg.nkb && row < p.n) sc_next = __half2float(srow[g + 1]);
-            ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+            ok = mbar_wait(acc_full(buf), use & 1u, wctl);
             if (!ok) break;
             tc_fence_after();
             if (active) {
@@ -636,7 +656,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
-                  acc[c + i] = fmaf(sc, NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]), acc[c + i]);
+                  acc[c + i] = fmaf(sc, NCAT ? fmaf(__uint_as_float(v2[i]), 0.0625f, __uint_as_float(v[i])) : __uint_as_float(v[i]), acc[c + i]);
               }
             }
             tc_fence_before();
@@ -657,7 +677,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               sc[j] = sc_next[j];
               sc_next[j] = (g + GB + j < sg.nkb && row < p.n) ? __half2float(srow[g + GB + j]) : 0.0f;
             }
-            ok = mbar_wait(acc_full(buf), use & 1u, &abort_flag, p.flags);
+            ok = mbar_wait(acc_full(buf), use & 1u, wctl);
             if (!ok) break;
             tc_fence_after();
             if (active) {
@@ -672,7 +692,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < CH; ++i)
-                      acc[c + i] = fmaf(sc[j], NCAT ? __uint_as_float(v[i]) + __uint_as_float(v2[i]) : __uint_as_float(v[i]),
+                      acc[c + i] = fmaf(sc[j], NCAT ? fmaf(__uint_as_float(v2[i]), 0.0625f, __uint_as_float(v[i])) : __uint_as_float(v[i]),
                                         acc[c + i]);
                   }
                 }
@@ -753,13 +773,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 // One block per token row m.  value[i] = bf16( prologue(x)[m][i] ) exactly as the matvec path stages it;
-// then planes[0][m][pos(i)] = hi, planes[1][m][pos(i)] = lo with value * 2^p = hi + lo, tok_scale[m] = 2^-p.
+// then planes[0][m][pos(i)] = hi = e4m3(value * 2^p) and planes[1][m][pos(i)] = the rest value * 2^p - hi, stored
+// as e5m2(rest) (LO16 false: wide tiles, read as an e5m2 operand) or as e4m3(16 * rest) (LO16 true: narrow
+// tiles, whose epilogue divides by 16); tok_scale[m] = 2^-p.
 // PERM (AQ4): inside every 32 consecutive k the even elements come first, then the odd ones, which is
 // the order the nibble conversion produces.
-template <bool PERM>
+template <bool PERM, bool LO16>
 __global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t x_dtype, uint64_t x_stride, uint32_t k,
-                                                         uint32_t prologue, float eps, uint8_t *planes,
-                                                         uint64_t plane_stride, float *tok_scale) {
+                                                         uint32_t prologue, float eps, const __nv_bfloat16 *gamma,
+                                                         uint8_t *planes, uint64_t plane_stride, float *tok_scale) {
   __shared__ float red_ss[8], red_mx[8];
   // the GEMM launched behind this kernel may set itself up now; it waits for this grid before reading
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -777,14 +799,17 @@ __global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t
     }
     return v;
   };
-  // pass 1: sum of squares (RMSNorm) and the largest magnitude
+  const bool weighted = prologue == ULLM_CUDA_PROLOGUE_RMSNORM && gamma != nullptr;
+  // pass 1: sum of squares (RMSNorm) and the largest magnitude (of x * gamma when there is a weight vector:
+  // the positive factor 1/rms and the final rounding are monotone, so this finds the largest staged magnitude)
   float ss = 0.0f, mx = 0.0f;
   for (uint32_t g = warp; g < groups; g += 8) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float v = pre(g * 128 + lane * 4 + j);
+      const uint32_t i = g * 128 + lane * 4 + j;
+      const float v = pre(i);
       ss = fmaf(v, v, ss);
-      mx = fmaxf(mx, fabsf(v));
+      mx = fmaxf(mx, weighted ? fabsf(v * __bfloat162float(gamma[i])) : fabsf(v));
     }
   }
 #pragma unroll
@@ -803,12 +828,14 @@ __global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t
     amax = fmaxf(amax, red_mx[w]);
   }
   const float inv = prologue == ULLM_CUDA_PROLOGUE_RMSNORM ? 1.0f / sqrtf(tot / (float)k + eps) : 1.0f;
-  amax = bf16r(amax * inv);  // rounding and the positive factor are monotone: this is the largest staged magnitude
+  // an upper bound of the largest staged magnitude (the staged value rounds (v * inv) * gamma, this rounds
+  // (v * gamma) * inv: at most a few ulp apart, and the top of the range below leaves a factor 1.75 of room)
+  amax = bf16r(amax * inv);
   int p = 0;
   if (amax > 0.0f && amax <= 3.0e38f) {
     int e;
     (void)frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
-    p = 8 - e;               // amax * 2^p in [128, 256)
+    p = 8 - e;               // amax * 2^p in [128, 256); e4m3 reaches 448
     p = p > 126 ? 126 : (p < -126 ? -126 : p);
   }
   const float up = ldexpf(1.0f, p);
@@ -818,13 +845,20 @@ __global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t
   for (uint32_t g = warp; g < groups; g += 8) {
     float xs[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) xs[j] = bf16r(pre(g * 128 + lane * 4 + j) * inv) * up;
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t i = g * 128 + lane * 4 + j;
+      const float v = pre(i) * inv;
+      xs[j] = bf16r(weighted ? v * __bfloat162float(gamma[i]) : v) * up;
+    }
     const uint32_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(xs[0], xs[1]), __NV_SATFINITE, __NV_E4M3);
     const uint32_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(xs[2], xs[3]), __NV_SATFINITE, __NV_E4M3);
     const float2 hf01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)h01, __NV_E4M3)));
     const float2 hf23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)h23, __NV_E4M3)));
-    const uint32_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(xs[0] - hf01.x, xs[1] - hf01.y), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(xs[2] - hf23.x, xs[3] - hf23.y), __NV_SATFINITE, __NV_E4M3);
+    const float ls = LO16 ? 16.0f : 1.0f;
+    const float2 r01 = make_float2((xs[0] - hf01.x) * ls, (xs[1] - hf01.y) * ls);
+    const float2 r23 = make_float2((xs[2] - hf23.x) * ls, (xs[3] - hf23.y) * ls);
+    const uint32_t l01 = __nv_cvt_float2_to_fp8x2(r01, __NV_SATFINITE, LO16 ? __NV_E4M3 : __NV_E5M2);
+    const uint32_t l23 = __nv_cvt_float2_to_fp8x2(r23, __NV_SATFINITE, LO16 ? __NV_E4M3 : __NV_E5M2);
     if (PERM) {
       // elements 4j..4j+3 of a 32-chunk (j = lane % 8): 4j and 4j+2 are even elements 2j, 2j+1 -> positions 2j, 2j+1;
       // 4j+1 and 4j+3 are odd elements 2j, 2j+1 -> positions 16+2j, 16+2j+1
@@ -917,14 +951,19 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   p.raw_stages = (uint32_t)rs;
   const size_t smem = ns * stage + rs * raw_stage + 1024;
   auto kern = gemm_kernel<ENC, TT, RT, KS>;
+  // function attributes are per device: raised once per (device, kernel)
   static std::mutex mu;
-  static bool configured = false;
+  static bool configured[kMaxDevices] = {};
   {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!configured[dev]) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
-      configured = true;
+      configured[dev] = true;
     }
   }
   // programmatic dependent launch: barrier setup and tensor-memory allocation overlap the kernel that
@@ -942,10 +981,16 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   return cudaLaunchKernelEx(&cfg, kern, wmap, xmap, p);
 }
 
+#ifdef ULLM_CUDA_TUNING
+// Tuning builds only (-DULLM_CUDA_TUNING): ULLM_CUDA_GEMM_TOKENS / _ROWS / _WHOLE / _STAGE_K override the tile
+// choices below.  The shipped library reads no environment variable.
 int env_int(const char *name) {
   const char *s = std::getenv(name);
   return s ? std::atoi(s) : 0;
 }
+#else
+constexpr int env_int(const char *) { return 0; }
+#endif
 
 int tile_tokens(uint32_t m, uint32_t enc) {
   static const int forced = env_int("ULLM_CUDA_GEMM_TOKENS");
@@ -1027,15 +1072,24 @@ Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
 constexpr size_t kStaticExtra = ULLM_CUDA_STATIC_SCRATCH_BYTES / 32 + 1024;
 
 cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &a, const Plan &pl, uint8_t *scratch,
-                     int *launches) {
+                     uint32_t *tile_counters, int *launches) {
+  if (encode_tiled() == nullptr) return cudaErrorNotSupported;  // the driver does not offer cuTensorMapEncodeTiled
   uint8_t *planes = scratch + pl.off_planes;
   float *tok = reinterpret_cast<float *>(scratch + pl.off_tok);
-  if (a.encoding == AQ4)
-    act_planes_kernel<true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, planes,
-                                                     (uint64_t)a.m * a.k, tok);
-  else
-    act_planes_kernel<false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, planes,
-                                                      (uint64_t)a.m * a.k, tok);
+  const __nv_bfloat16 *gamma = static_cast<const __nv_bfloat16 *>(a.norm_weight);
+  const bool lo16 = pl.tt <= 64;  // narrow tiles: the two planes are one operand, the rest plane is e4m3(16 * rest)
+  const uint64_t pstride = (uint64_t)a.m * a.k;
+  if (a.encoding == AQ4) {
+    if (lo16)
+      act_planes_kernel<true, true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+    else
+      act_planes_kernel<true, false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+  } else {
+    if (lo16)
+      act_planes_kernel<false, true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+    else
+      act_planes_kernel<false, false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   ++*launches;
@@ -1051,8 +1105,12 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   p.sk_ctas = pl.sk_ctas;
   p.m_fastest = pl.m_fastest ? 1u : 0u;
   p.partial = pl.sk_ctas == 0 ? nullptr : reinterpret_cast<float *>(scratch + pl.off_partial);
-  p.tile_counters = ctx->tile_counters;
+  p.tile_counters = tile_counters;
   p.flags = ctx->device_flags;
+  p.abort_word = a.abort_word != nullptr ? a.abort_word : ctx->abort_word;
+  p.wait_ns = (uint64_t)(a.wait_limit_ms != 0 ? a.wait_limit_ms : kDefaultWaitLimitMs) * 1000000ull;
+  p.residual = pair ? nullptr : a.residual;
+  p.res_stride = a.res_stride;
   if (pair) {  // gate|up to scratch as bf16, combined afterwards
     p.y = scratch + pl.off_pair;
     p.y_stride = a.n;
@@ -1105,27 +1163,20 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
 
 }  // namespace
 
-bool gemm_supports(const Context *, const LinearArgs &a, const char **why) {
+// A shape-only answer: no handle, driver or device is consulted (the weight span is 16-byte aligned by the
+// buffer rules; a driver without cuTensorMapEncodeTiled is reported when the op is enqueued).
+bool gemm_supports(const LinearArgs &a, const char **why) {
   if (a.k % 128 != 0) {
     *why = "the GEMM kernel needs K to be a multiple of 128";
-    return false;
-  }
-  if (reinterpret_cast<uintptr_t>(a.w) % 16 != 0) {
-    *why = "the GEMM kernel needs the weight values 16-byte aligned";
-    return false;
-  }
-  if (encode_tiled() == nullptr) {
-    *why = "cuTensorMapEncodeTiled is not available from this driver";
     return false;
   }
   return true;
 }
 
-// Scratch owned by the context: grows on demand, reused by every GEMM on that context.
-static cudaError_t ensure_scratch(const Context *cctx, cudaStream_t stream, size_t bytes, void **out) {
-  Context *ctx = const_cast<Context *>(cctx);
-  std::lock_guard<std::mutex> g(ctx->mutex);
-  if ((ctx->tile_counters == nullptr || ctx->scratch_bytes < bytes) && stream != nullptr) {
+// Scratch owned by a queue: grows on demand, reused by every GEMM enqueued on that queue (which orders them).
+static cudaError_t ensure_scratch(GemmScratch *sc, cudaStream_t stream, size_t bytes, void **out) {
+  std::lock_guard<std::mutex> g(sc->mutex);
+  if ((sc->tile_counters == nullptr || sc->bytes < bytes) && stream != nullptr) {
     // an allocation would invalidate a stream capture in progress: refuse instead (run the same linear once
     // outside the capture, or create the stack, which reserves its scratch, before capturing)
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -1133,30 +1184,36 @@ static cudaError_t ensure_scratch(const Context *cctx, cudaStream_t stream, size
     if (e != cudaSuccess) return e;
     if (cs != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
   }
-  if (ctx->tile_counters == nullptr) {
-    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&ctx->tile_counters), kMaxCounterTiles * sizeof(uint32_t));
+  if (sc->tile_counters == nullptr) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&sc->tile_counters), kMaxCounterTiles * sizeof(uint32_t));
     if (e != cudaSuccess) return e;
-    e = cudaMemset(ctx->tile_counters, 0, kMaxCounterTiles * sizeof(uint32_t));
+    e = cudaMemset(sc->tile_counters, 0, kMaxCounterTiles * sizeof(uint32_t));
     if (e != cudaSuccess) return e;
   }
-  if (ctx->scratch_bytes < bytes) {
-    if (ctx->scratch != nullptr) {
-      cudaError_t e = cudaFree(ctx->scratch);
-      if (e != cudaSuccess) return e;
-      ctx->scratch = nullptr;
-      ctx->scratch_bytes = 0;
+  if (sc->bytes < bytes) {
+    if (sc->ptr != nullptr) {
+      // earlier GEMMs of this queue may still be reading the old area: it is released behind them
+      void *old = sc->ptr;
+      sc->ptr = nullptr;
+      sc->bytes = 0;
+      int dev = 0;
+      (void)cudaGetDevice(&dev);
+      if (stream != nullptr)
+        (void)retire_behind(dev, stream, [old] { (void)cudaFree(old); });
+      else
+        (void)cudaFree(old);
     }
-    cudaError_t e = cudaMalloc(&ctx->scratch, bytes);
+    cudaError_t e = cudaMalloc(&sc->ptr, bytes);
     if (e != cudaSuccess) return e;
-    ctx->scratch_bytes = bytes;
+    sc->bytes = bytes;
   }
-  *out = ctx->scratch;
+  *out = sc->ptr;
   return cudaSuccess;
 }
 
-cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes) {
+cudaError_t gemm_reserve_scratch(GemmScratch *sc, size_t bytes) {
   void *unused = nullptr;
-  return ensure_scratch(ctx, nullptr, bytes, &unused);
+  return ensure_scratch(sc, nullptr, bytes, &unused);
 }
 
 size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a) { return make_plan(ctx, a, true).bytes; }
@@ -1167,7 +1224,6 @@ size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a) { return make
 static __device__ __align__(256) uint8_t g_static_scratch[ULLM_CUDA_STATIC_SCRATCH_BYTES + kStaticExtra];
 
 static cudaError_t static_scratch_address(int device, uint8_t **out) {
-  constexpr int kMaxDevices = 64;
   static std::mutex mu;
   static uint8_t *address[kMaxDevices] = {};
   if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
@@ -1193,17 +1249,17 @@ int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const Li
   *err = static_scratch_address(ctx->device, &scratch);
   if (*err != cudaSuccess) return -1;
   int launches = 0;
-  *err = run_plan(ctx, stream, a, pl, scratch, &launches);
+  *err = run_plan(ctx, stream, a, pl, scratch, nullptr, &launches);  // whole tiles only: no arrival counters
   return *err == cudaSuccess ? launches : -1;
 }
 
-int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
+int launch_gemm(const Context *ctx, GemmScratch *scratch, cudaStream_t stream, const LinearArgs &a, cudaError_t *err) {
   const Plan pl = make_plan(ctx, a, true);
   void *s = nullptr;
-  *err = ensure_scratch(ctx, stream, pl.bytes, &s);
+  *err = ensure_scratch(scratch, stream, pl.bytes, &s);
   if (*err != cudaSuccess) return -1;
   int launches = 0;
-  *err = run_plan(ctx, stream, a, pl, static_cast<uint8_t *>(s), &launches);
+  *err = run_plan(ctx, stream, a, pl, static_cast<uint8_t *>(s), scratch->tile_counters, &launches);
   return *err == cudaSuccess ? launches : -1;
 }
 

@@ -12,9 +12,11 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <limits>
 #include <mutex>
 #include <string>
@@ -82,6 +84,11 @@ constexpr uint32_t kMagicContext = 0x63747831U, kMagicQueue = 0x71756531U, kMagi
                    kMagicCompletion = 0x636d7031U, kMagicGraph = 0x67726131U, kMagicComm = 0x636f6d31U,
                    kMagicStack = 0x73746b31U;
 
+constexpr int kMaxDevices = 64;
+constexpr uint32_t kDefaultWaitLimitMs = 20000;
+
+struct Queue;
+
 struct Context {
   uint32_t magic = kMagicContext;
   int device = 0;
@@ -90,12 +97,25 @@ struct Context {
   size_t smem_optin = 0;
   uint32_t *host_flags = nullptr;    // [16] words, mapped pinned memory
   uint32_t *device_flags = nullptr;  // device view of host_flags: kernels set a word when a bounded wait expires
-  void *scratch = nullptr;           // grow-only device scratch of the GEMM path (prologue output, gate|up)
-  size_t scratch_bytes = 0;
-  uint32_t *tile_counters = nullptr;  // split-K arrival counters of the GEMM path, zero between launches
+  // Device-resident abort word: set (with the flag word) by the first wait that gives up, read by every
+  // later wait before it starts polling, so that all the work queued behind an expired wait unwinds in
+  // about one limit instead of one limit per wait.  Cleared by the completion wait that reports it.
+  uint32_t *abort_word = nullptr;
+  std::atomic<uint32_t> wait_limit_ms{kDefaultWaitLimitMs};  // limit of every device-side wait
   std::mutex mutex;
   std::vector<cudaEvent_t> event_pool;
+  std::vector<Queue *> queues;  // live queues (guarded by mutex): buffer_free checks that they are idle
   std::atomic<uint64_t> live_children{0};
+};
+
+// Device scratch of the GEMM path (activation planes, token scales, gate|up pairs, split-K partials and the
+// split-K arrival counters).  One per queue: linears enqueued on different queues may overlap on the GPU, so
+// they must not share staging memory or counters.
+struct GemmScratch {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  uint32_t *tile_counters = nullptr;  // zero between launches
+  std::mutex mutex;
 };
 
 struct Queue {
@@ -108,6 +128,7 @@ struct Queue {
   uint64_t total_dispatch = 0;
   bool capturing = false;
   void *staging = nullptr;  // pinned, kStagingBytes
+  GemmScratch scratch;
 };
 constexpr size_t kStagingBytes = size_t(16) << 20;
 
@@ -120,7 +141,9 @@ struct Buffer {
 
 struct Completion {
   uint32_t magic = kMagicCompletion;
-  Queue *queue = nullptr;
+  Queue *queue = nullptr;  // may have been destroyed since: check the registry before use
+  Context *ctx = nullptr;
+  cudaStream_t stream = nullptr;
   cudaEvent_t event = nullptr;
   uint64_t dispatch_count = 0;
   uint64_t copy_count = 0;
@@ -190,6 +213,11 @@ ullm_status_t resolve(const ullm_cuda_tensor_t &t, uint64_t bytes, uint64_t alig
 
 // Queue acquisition for an op: valid handle, right device made current.
 ullm_status_t begin_op(ullm_cuda_queue_t *queue, sink_t *sink, Queue **out) noexcept;
+// false (with *status set) while resources wait too long to be retired: new work is refused.
+bool submissions_open(sink_t *sink, ullm_status_t *status) noexcept;
+// Runs `release` now if `stream` is observed idle, else in the background once a fence behind the
+// stream's current work is reached.  Never blocks.  false = nothing can watch the fence (abandoned).
+bool retire_behind(int device, cudaStream_t stream, std::function<void()> release) noexcept;
 // Post-launch check + accounting.
 ullm_status_t end_launch(Queue *q, sink_t *sink, const char *what, uint64_t kernels = 1) noexcept;
 
@@ -219,12 +247,16 @@ inline uint64_t dtype_bytes(uint32_t dtype) {
 // A row-parallel matvec writes every fp32 partial output together with a 32-bit tag as ONE 8-byte
 // store into a slot of EVERY rank's symmetric buffer (plain peer stores over NVLink; 8-byte stores
 // are single-copy atomic, so a reader that sees the tag sees the value: no fence, no flag word, no
-// atomic).  The next kernel on each rank sums the ranks' slots while it stages its activations
-// (each CTA a share, published with the same tag to a local buffer all CTAs then read),
-// re-reading (time-bounded) any pair whose tag is not yet the expected one.  The tag is
-// step_counter * uses_per_step + use + 1, where a one-thread kernel bumps step_counter once per
-// step; two slot sets alternate per use of a site so that a fast rank never overwrites what a slow
-// rank is still reading.
+// atomic).  The next kernel on each rank sums the ranks' slots while it stages its activations,
+// re-reading (time-bounded) any pair whose tag is not yet the expected one: either every CTA reads
+// all ranks' slots itself, or (cluster launch) each CTA of a thread-block cluster sums a share and
+// hands it to the others through distributed shared memory, so that the slots are read once per
+// cluster.  The tag is step_counter * uses_per_step + use + 1, where a one-thread kernel bumps
+// step_counter once per step; two slot sets alternate per use of a site so that a fast rank never
+// overwrites what a slow rank is still reading.
+// Tag arithmetic is modulo 2^32.  A slot is rewritten every second use of its site, so the tag found in
+// it is always the expected one or the one from two uses earlier; the two can only coincide 2^32 uses
+// apart, and by the first wrap no slot still holds its initial zero.  Wrap-around is therefore harmless.
 constexpr int kMaxPeers = 8;
 struct PushOut {       // producer side
   uint8_t *peer_base[kMaxPeers];  // every rank's symmetric buffer as mapped here
@@ -238,12 +270,12 @@ struct PushIn {        // consumer side
   const uint8_t *local_base;
   uint64_t slot_off[2];
   uint64_t slot_stride;
-                                  // into it, then every CTA stages from it (so the ranks' slots are read once
-                                  // per GPU, not once per CTA)
   const uint32_t *step_counter;
   uint32_t uses_per_step, use;
-  float *reduced_out;             // optional: CTA 0 also stores the summed rows here
+  const float *residual;          // optional f32 [M, K]: the staged input is residual + sum over ranks
+  float *reduced_out;             // optional f32 [M, K]: one thread block (or cluster) also stores that input here
   uint32_t tp = 0;
+  uint32_t cluster = 0;           // 0: every thread block reads all ranks' slots; else blocks per cluster sharing one reading
 };
 
 // ---- internal launchers (raw device pointers; arguments already validated) -----
@@ -261,6 +293,11 @@ struct LinearArgs {
   uint32_t prologue = 0;
   uint32_t epilogue = 0;
   float rms_eps = 1e-5f;
+  const void *norm_weight = nullptr;  // RMSNorm prologue: bf16 gamma[K], or null
+  const float *residual = nullptr;    // f32 [M, res_stride]: y = x . W'^T + residual (may alias y)
+  uint64_t res_stride = 0;
+  uint32_t wait_limit_ms = kDefaultWaitLimitMs;  // limit of the kernel's device-side waits
+  uint32_t *abort_word = nullptr;                // the context's device-resident abort word
   PushOut push_out{};  // matvec only: write the fp32 output into every rank's slot instead of y
   PushIn push_in{};    // matvec only: the input is the sum of the ranks' slots
 };
@@ -269,23 +306,23 @@ struct LinearArgs {
 int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
 bool matvec_supports(const LinearArgs &a, const char **why);
 
-int launch_gemm(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+// `scratch` is the staging memory of the queue whose stream is given (grown on demand, not during capture).
+int launch_gemm(const Context *ctx, GemmScratch *scratch, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
 // The GEMM path with its activation staging area in a fixed file-scope device array (no allocation).
 // Returns kernels launched, -1 with *err set, or -2 when the arguments do not fit the array.
 int launch_gemm_static_scratch(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
 // Scratch bytes launch_gemm needs for these arguments, and a way to reserve them ahead of
 // time (the scratch may not grow while a stream is being captured).
 size_t gemm_scratch_bytes(const Context *ctx, const LinearArgs &a);
-cudaError_t gemm_reserve_scratch(const Context *ctx, size_t bytes);
-bool gemm_supports(const Context *ctx, const LinearArgs &a, const char **why);
+cudaError_t gemm_reserve_scratch(GemmScratch *scratch, size_t bytes);
+// Shape-only answer (no device, no driver): `a.w` may be null.
+bool gemm_supports(const LinearArgs &a, const char **why);
 // Kernel behind ULLM_CUDA_KERNEL_AUTO when both serve the shape.  Measured on weights larger than L2: the
 // tensor-core path streams FP8 weights faster than the CUDA-core matvec from two tokens on (5.2 vs 3.7 TB/s
 // at M=2, 2.7 vs 0.84 at M=8); for AQ4 it wins from five tokens on (1.6 vs 1.0 TB/s at M=8, 1.6 vs 1.9 at M=4).
 inline bool auto_prefers_gemm(const LinearArgs &a) {
   return a.encoding == ULLM_CUDA_ENCODING_FP8_CHANNEL ? a.m >= 2 : a.m >= 5;
 }
-
-int launch_prologue(cudaStream_t stream, const LinearArgs &a, void *x_bf16_out, cudaError_t *err);
 
 void launch_synth_weights(cudaStream_t s, uint64_t seed, uint64_t tensor_id, uint64_t first, uint64_t count,
                           float std, float *out);
@@ -303,7 +340,11 @@ void launch_dequantize(cudaStream_t s, uint32_t encoding, const uint8_t *values,
 
 // comm internals used by the stack
 struct Comm;
+// Collective: every rank calls it with the same size.  true = this rank's zeroed symmetric buffer of at least
+// `bytes` is mapped on every rank and reserved for the caller until comm_sym_release; false = not available
+// (no peer access, or another user holds it): the same verdict on every rank.
 bool comm_sym_setup(Comm *c, size_t bytes, std::string *why);
+void comm_sym_release(Comm *c);
 bool comm_p2p(const Comm *c);
 uint8_t *comm_sym_ptr(const Comm *c, uint32_t peer);
 size_t comm_sym_bytes(const Comm *c);

@@ -39,6 +39,14 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   if (desc->kernel > ULLM_CUDA_KERNEL_GEMM) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "unknown kernel id");
   if (desc->prologue == ULLM_CUDA_PROLOGUE_RMSNORM && !(desc->rms_eps >= 0.0f))
     return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "rms_eps must be non-negative");
+  if (desc->norm_weight.buffer != nullptr && desc->prologue != ULLM_CUDA_PROLOGUE_RMSNORM)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "norm_weight is only meaningful with the RMSNorm prologue");
+  if (desc->residual.buffer != nullptr && desc->epilogue == ULLM_CUDA_EPILOGUE_SWIGLU)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "a residual cannot be combined with the SwiGLU epilogue");
+  // Strides come from the caller: bound them so that no span computation below can wrap around.
+  constexpr uint64_t kMaxStride = uint64_t(1) << 40;
+  if (desc->input_row_stride > kMaxStride || desc->output_row_stride > kMaxStride || desc->residual_row_stride > kMaxStride)
+    return write_error(sink, ULLM_STATUS_CUDA_OUT_OF_RANGE, "a row stride above 2^40 elements is not addressable");
 
   if (need_buffers) {
     WeightPtrs wp;
@@ -75,21 +83,47 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   a.y_stride = desc->output_row_stride == 0 ? out_cols : desc->output_row_stride;
   if (a.x_stride < in_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "input row stride is shorter than a row");
   if (a.y_stride < out_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output row stride is shorter than a row");
+  a.res_stride = desc->residual_row_stride == 0 ? out_cols : desc->residual_row_stride;
+  if (a.res_stride < out_cols) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "residual row stride is shorter than a row");
 
   if (need_buffers) {
     const uint64_t xb = dtype_bytes(a.x_dtype), yb = dtype_bytes(a.y_dtype);
+    // ((m - 1) * stride + cols) * bytes, checked: m <= 2^20, stride <= 2^40, cols < 2^32, bytes <= 4
+    auto span = [&](uint64_t stride, uint64_t cols, uint64_t bytes, uint64_t *out_bytes) {
+      uint64_t v = 0;
+      return !__builtin_mul_overflow(desc->m - 1, stride, &v) && !__builtin_add_overflow(v, cols, &v) &&
+             !__builtin_mul_overflow(v, bytes, out_bytes);
+    };
+    uint64_t x_bytes = 0, y_bytes = 0, r_bytes = 0;
+    if (!span(a.x_stride, in_cols, xb, &x_bytes) || !span(a.y_stride, out_cols, yb, &y_bytes) ||
+        !span(a.res_stride, out_cols, 4, &r_bytes))
+      return write_error(sink, ULLM_STATUS_CUDA_OUT_OF_RANGE, "a tensor span does not fit 64 bits");
     void *x = nullptr, *y = nullptr;
-    st = resolve(desc->input, ((desc->m - 1) * a.x_stride + in_cols) * xb, xb, ctx, "linear input", sink, &x);
+    st = resolve(desc->input, x_bytes, xb, ctx, "linear input", sink, &x);
     if (st != ULLM_STATUS_OK) return st;
-    st = resolve(desc->output, ((desc->m - 1) * a.y_stride + out_cols) * yb, yb, ctx, "linear output", sink, &y);
+    st = resolve(desc->output, y_bytes, yb, ctx, "linear output", sink, &y);
     if (st != ULLM_STATUS_OK) return st;
     a.x = x;
     a.y = y;
+    if (desc->norm_weight.buffer != nullptr) {
+      void *g = nullptr;
+      st = resolve(desc->norm_weight, w.k * 2, 16, ctx, "norm weight", sink, &g);
+      if (st != ULLM_STATUS_OK) return st;
+      a.norm_weight = g;
+    }
+    if (desc->residual.buffer != nullptr) {
+      void *r = nullptr;
+      st = resolve(desc->residual, r_bytes, 4, ctx, "residual", sink, &r);
+      if (st != ULLM_STATUS_OK) return st;
+      a.residual = static_cast<const float *>(r);
+    }
+    a.wait_limit_ms = ctx->wait_limit_ms.load();
+    a.abort_word = ctx->abort_word;
   }
 
   const char *why_mv = "", *why_gemm = "";
   const bool mv = matvec_supports(a, &why_mv);
-  const bool gm = gemm_supports(ctx, a, &why_gemm);
+  const bool gm = gemm_supports(a, &why_gemm);
   uint32_t kernel = desc->kernel;
   if (kernel == ULLM_CUDA_KERNEL_AUTO)
     kernel = (mv && !(gm && auto_prefers_gemm(a))) ? ULLM_CUDA_KERNEL_MATVEC : (gm ? ULLM_CUDA_KERNEL_GEMM : 0u);
@@ -103,9 +137,11 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
 }
 
 static ullm_status_t enqueue_resolved(Queue *q, const Resolved &r, sink_t *sink) {
+  ullm_status_t refused = ULLM_STATUS_OK;
+  if (!submissions_open(sink, &refused)) return refused;
   cudaError_t e = cudaSuccess;
   const int launched = r.kernel == ULLM_CUDA_KERNEL_MATVEC ? launch_matvec(q->ctx, q->stream, r.args, &e)
-                                                           : launch_gemm(q->ctx, q->stream, r.args, &e);
+                                                           : launch_gemm(q->ctx, &q->scratch, q->stream, r.args, &e);
   if (launched < 0) return cuda_error(sink, e, "linear kernel launch");
   if (launched == 0)
     return write_error(sink, ULLM_STATUS_CUDA_ZERO_DISPATCH, "linear op launched no kernel");
@@ -166,7 +202,8 @@ ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_queue_t *queue,
   st = resolve_linear(desc, q->ctx, true, sink, &r);
   if (st != ULLM_STATUS_OK) return st;
   const char *why = "";
-  if (!gemm_supports(q->ctx, r.args, &why)) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "gemm: %s", why);
+  if (!gemm_supports(r.args, &why)) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "gemm: %s", why);
+  if (!submissions_open(sink, &st)) return st;
   cudaError_t e = cudaSuccess;
   const int launched = launch_gemm_static_scratch(q->ctx, q->stream, r.args, &e);
   if (launched == -2)
@@ -177,6 +214,121 @@ ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_queue_t *queue,
   if (launched < 0) return cuda_error(sink, e, "allocation-free linear launch");
   return end_launch(q, sink, "allocation-free linear launch", static_cast<uint64_t>(launched));
   ULLM_ENTRY_END("linear enqueue (static scratch)")
+}
+
+// Common part of the two single-op halves of the fused all-reduce: the slots' span and the step word.
+static ullm_status_t resolve_slots(const ullm_cuda_slots_t *sl, const Context *ctx, uint64_t pairs, sink_t *sink,
+                                   uint8_t **base) {
+  ullm_status_t st = validate_struct(sl, sink, "slots descriptor");
+  if (st != ULLM_STATUS_OK) return st;
+  if (sl->ranks == 0 || sl->ranks > static_cast<uint32_t>(kMaxPeers))
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "ranks must be between 1 and 8");
+  if (sl->rank >= sl->ranks) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "rank must be below ranks");
+  if (sl->gather > 1) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "gather must be 0 or 1");
+  if (sl->rank_stride_bytes % 16 != 0 || sl->rank_stride_bytes < pairs * 8 || sl->rank_stride_bytes > (uint64_t(1) << 40))
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "rank_stride_bytes must be a multiple of 16 that holds M * cols pairs");
+  void *p = nullptr;
+  st = resolve(sl->slots, (sl->ranks - 1) * sl->rank_stride_bytes + pairs * 8, 16, ctx, "slots", sink, &p);
+  if (st != ULLM_STATUS_OK) return st;
+  *base = static_cast<uint8_t *>(p);
+  return ULLM_STATUS_OK;
+}
+
+ullm_status_t ullm_cuda_linear_enqueue_partial(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                               const ullm_cuda_slots_t *slots, ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "linear descriptor is null");
+  Queue *q = nullptr;
+  st = begin_op(queue, sink, &q);
+  if (st != ULLM_STATUS_OK) return st;
+  Resolved r;
+  st = resolve_linear(desc, q->ctx, true, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc->epilogue != ULLM_CUDA_EPILOGUE_NONE || desc->residual.buffer != nullptr)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "a partial linear takes neither an epilogue nor a residual");
+  const char *why = "";
+  if (!matvec_supports(r.args, &why)) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "matvec: %s", why);
+  uint8_t *base = nullptr;
+  st = resolve_slots(slots, q->ctx, static_cast<uint64_t>(r.args.m) * r.args.n, sink, &base);
+  if (st != ULLM_STATUS_OK) return st;
+  if (!submissions_open(sink, &st)) return st;
+  LinearArgs a = r.args;
+  // one device stands for every rank: each "peer" is the same buffer, the slot is chosen by rank * stride
+  for (uint32_t p = 0; p < slots->ranks; ++p) a.push_out.peer_base[p] = base;
+  a.push_out.slot_off[0] = a.push_out.slot_off[1] = 0;
+  a.push_out.slot_stride = slots->rank_stride_bytes;
+  a.push_out.step_counter = q->ctx->abort_word + 1;  // a word that stays zero: the tag is use + 1
+  a.push_out.uses_per_step = 0;
+  a.push_out.use = slots->tag - 1u;
+  a.push_out.tp = 1;  // one store per value (all "peers" are this buffer)
+  a.push_out.rank = slots->rank;
+  cudaError_t e = cudaSuccess;
+  const int launched = launch_matvec(q->ctx, q->stream, a, &e);
+  if (launched < 0) return cuda_error(sink, e, "partial linear launch");
+  return end_launch(q, sink, "partial linear launch", static_cast<uint64_t>(launched));
+  ULLM_ENTRY_END("linear enqueue (partial)")
+}
+
+ullm_status_t ullm_cuda_linear_enqueue_reduced(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,
+                                               const ullm_cuda_slots_t *slots, ullm_cuda_tensor_t reduced_out,
+                                               ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "linear descriptor is null");
+  Queue *q = nullptr;
+  st = begin_op(queue, sink, &q);
+  if (st != ULLM_STATUS_OK) return st;
+  // the residual of this entry belongs to the input ([M, K]): validate the rest of the descriptor without it
+  ullm_cuda_linear_desc_t d = *desc;
+  d.residual.buffer = nullptr;
+  d.residual.offset_bytes = 0;
+  d.residual_row_stride = 0;
+  Resolved r;
+  st = resolve_linear(&d, q->ctx, true, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  if (desc->prologue == ULLM_CUDA_PROLOGUE_SWIGLU)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "a reduced linear takes the NONE or RMSNORM prologue");
+  if (r.args.k % 8 != 0) return write_error(sink, ULLM_STATUS_UNSUPPORTED, "a reduced linear needs K to be a multiple of 8");
+  const char *why = "";
+  if (!matvec_supports(r.args, &why)) return errorf(sink, ULLM_STATUS_UNSUPPORTED, "matvec: %s", why);
+  uint8_t *base = nullptr;
+  const uint64_t elems = static_cast<uint64_t>(r.args.m) * r.args.k;
+  st = resolve_slots(slots, q->ctx, elems, sink, &base);
+  if (st != ULLM_STATUS_OK) return st;
+  LinearArgs a = r.args;
+  if (desc->residual.buffer != nullptr) {
+    if (desc->residual_row_stride != 0 && desc->residual_row_stride != r.args.k)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "the input residual of a reduced linear is dense [M, K]");
+    void *p = nullptr;
+    st = resolve(desc->residual, elems * 4, 16, q->ctx, "input residual", sink, &p);
+    if (st != ULLM_STATUS_OK) return st;
+    a.push_in.residual = static_cast<const float *>(p);
+  }
+  if (reduced_out.buffer != nullptr) {
+    void *p = nullptr;
+    st = resolve(reduced_out, elems * 4, 16, q->ctx, "reduced output", sink, &p);
+    if (st != ULLM_STATUS_OK) return st;
+    a.push_in.reduced_out = static_cast<float *>(p);
+  }
+  if (!submissions_open(sink, &st)) return st;
+  a.push_in.local_base = base;
+  a.push_in.slot_off[0] = a.push_in.slot_off[1] = 0;
+  a.push_in.slot_stride = slots->rank_stride_bytes;
+  a.push_in.step_counter = q->ctx->abort_word + 1;
+  a.push_in.uses_per_step = 0;
+  a.push_in.use = slots->tag - 1u;
+  a.push_in.tp = slots->ranks;
+  a.push_in.cluster = slots->gather ? 8u : 0u;
+  cudaError_t e = cudaSuccess;
+  const int launched = launch_matvec(q->ctx, q->stream, a, &e);
+  if (launched < 0) return cuda_error(sink, e, "reduced linear launch");
+  return end_launch(q, sink, "reduced linear launch", static_cast<uint64_t>(launched));
+  ULLM_ENTRY_END("linear enqueue (reduced)")
 }
 
 ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, const ullm_cuda_linear_desc_t *desc,

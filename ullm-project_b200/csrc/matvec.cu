@@ -35,9 +35,14 @@ int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, 
   p.epilogue = a.epilogue;
   p.rms_eps = a.rms_eps;
   p.k_pad = pad_k(a.k, a.encoding);
+  p.norm_weight = a.norm_weight;
+  p.residual = a.residual;
+  p.res_stride = a.res_stride;
   p.po = a.push_out;
   p.pi = a.push_in;
   p.flags = ctx->device_flags;
+  p.abort_word = a.abort_word != nullptr ? a.abort_word : ctx->abort_word;
+  p.wait_ns = (uint64_t)(a.wait_limit_ms != 0 ? a.wait_limit_ms : kDefaultWaitLimitMs) * 1000000ull;
   const uint64_t xe = a.x_dtype == ULLM_CUDA_DTYPE_F32 ? 4 : 2;
   const bool aligned = reinterpret_cast<uintptr_t>(a.x) % 16 == 0 && (a.x_stride * xe) % 16 == 0 &&
                        (a.k * xe) % 16 == 0 && a.k % 8 == 0;

@@ -33,7 +33,10 @@
 //     with DP4A (4 MACs per instruction):  sum x*q = sum x*u - 8*sum x, all in int32; one
 //     I2F and one FFMA per piece apply 2^-shift * fp16 group scale.  A piece never
 //     straddles a scale group of 128.
-//   * K is reduced across the lanes of one warp with shuffles.
+//   * K is reduced across the lanes of one warp with shuffles.  For matrices with too few rows to give
+//     every warp a row group, a row's K range is cut into S slices handled by S consecutive warps whose
+//     partial sums meet in shared memory (named barrier per warp set, fixed summation order).
+//   * RMSNorm takes an optional bf16 weight vector; an optional f32 residual is added to the result.
 // Algorithmic bytes per launch: N*K (FP8) or N*K/2 + N*K/64 (AQ4) weight bytes
 // + scales + M*K*2 in + M*N*2 out.
 #pragma once
@@ -50,8 +53,12 @@ namespace ullm {
 namespace matvec_impl {
 
 constexpr int kMaxWarps = 32;
+constexpr int kMaxClusterBlocks = 16;  // largest cluster the gather is laid out for
 // Kernel flavours: plain, input = sum of the ranks' slots, output = push into every rank's slot.
-constexpr int kModePlain = 0, kModePushIn = 1, kModePushOut = 2;
+// kModePushInCluster: as kModePushIn, but the blocks of a thread-block cluster each sum a share of the slots and
+// hand it to the others through distributed shared memory.
+constexpr int kModePlain = 0, kModePushIn = 1, kModePushOut = 2, kModePushInCluster = 3;
+constexpr uint32_t kFlagMatvecWait = 4u;
 constexpr uint32_t AQ4 = ULLM_CUDA_ENCODING_AQ4;
 constexpr uint32_t FP8 = ULLM_CUDA_ENCODING_FP8_CHANNEL;
 
@@ -87,15 +94,23 @@ struct Params {
   float rms_eps;
   uint32_t k_pad;   // K rounded up to a whole warp iteration
   uint32_t vec_ok;  // activation rows allow 16-byte loads
+  const void *norm_weight;  // bf16 gamma[K] of the RMSNorm prologue, or null
+  const float *residual;    // f32 [M, res_stride] added to the result, or null
+  uint64_t res_stride;
   PushOut po;       // tp != 0: the fp32 output goes into every rank's slot (fused all-reduce, producer half)
   PushIn pi;        // tp != 0: the input is the sum of the ranks' slots (consumer half)
   uint32_t *flags;  // device view of the context's error words
+  uint32_t *abort_word;  // device-resident: non-zero once any wait of the context has given up
+  uint64_t wait_ns;      // limit of a wait for a peer's data
 };
 
-// Reads N 16-byte words of {value, tag, value, tag} until every tag equals `want` (time-bounded:
-// on expiry the context is flagged and whatever was read is used).
+// Reads N 16-byte words of {value, tag, value, tag} until every tag equals `want`.  Time-bounded: when the
+// limit runs out the context is flagged, the device-resident abort word is set and whatever was read is used
+// (the host reports the results as invalid).  A wait that finds the abort word already set gives up at once, so
+// all the work queued behind an expired wait unwinds in about one limit.
 template <int N>
 __device__ __forceinline__ void poll_pairs(const Params &p, const uint4 *src, uint32_t want, uint4 (&q)[N]) {
+  if (p.abort_word != nullptr && *reinterpret_cast<volatile uint32_t *>(p.abort_word) != 0u) return;
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
 #pragma unroll
@@ -112,20 +127,55 @@ __device__ __forceinline__ void poll_pairs(const Params &p, const uint4 *src, ui
       uint64_t now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
       if (t0 == 0) t0 = now;
-      if (now - t0 > 20ull * 1000ull * 1000ull * 1000ull) {
-        if (p.flags != nullptr) atomicOr(p.flags, 4u);
+      const bool aborted = p.abort_word != nullptr && *reinterpret_cast<volatile uint32_t *>(p.abort_word) != 0u;
+      if (aborted || now - t0 > p.wait_ns) {
+        if (p.abort_word != nullptr) atomicOr(p.abort_word, 1u);
+        if (p.flags != nullptr) atomicOr(p.flags, kFlagMatvecWait);
         return;
       }
     }
   }
 }
 
+// ---- thread-block cluster helpers (distributed shared memory) ----------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of `smem_addr` (a shared::cta address of this block) in block `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_block(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// every thread of every block of the cluster; the stores above are visible to all blocks afterwards
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // x[m][k .. k+8) (k % 8 == 0, k + 8 <= row length) as eight packed bf16 values; fp32
 // inputs are rounded to bf16 here (the op is defined on bf16 activations).
 template <int MODE, bool PAIR = false>
-__device__ __forceinline__ uint4 load8_packed(const Params &p, uint32_t m, uint32_t k) {
+__device__ __forceinline__ uint4 load8_packed(const Params &p, uint32_t m, uint32_t k, const uint32_t *gathered = nullptr) {
   uint32_t w[4];
-  if (MODE == kModePushIn) {
+  if (MODE == kModePushInCluster) {
+    // the cluster has gathered the summed rows as packed bf16 [M][K] in this block's shared memory
+    return *reinterpret_cast<const uint4 *>(gathered + ((uint64_t)m * p.k + k) / 2);
+  } else if (MODE == kModePushIn) {
     // fused all-reduce, consumer half: sum the ranks' slots, {value, tag} pairs, in rank order (deterministic).
     // With PAIR (kernels that have the registers: 640 threads or fewer) two ranks' words are requested together,
     // so a unit costs tp/2 round trips to L2 rather than tp; a word whose tag is not there yet is polled on its own.
@@ -133,8 +183,14 @@ __device__ __forceinline__ uint4 load8_packed(const Params &p, uint32_t m, uint3
     const uint32_t want = use_global + 1u;
     const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u] + ((uint64_t)m * p.k + k) * 8;
     float v[8];
+    if (p.pi.residual != nullptr) {  // residual first, then the ranks in rank order
+      const float4 *rs = reinterpret_cast<const float4 *>(p.pi.residual + (uint64_t)m * p.k + k);
+      const float4 a = rs[0], b = rs[1];
+      v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
 #pragma unroll
     for (uint32_t r = 0; r < (uint32_t)kMaxPeers; r += PAIR ? 2 : 1) {
       if (r < p.pi.tp) {
@@ -239,13 +295,22 @@ __device__ __forceinline__ void finish8(const Params &p, uint32_t m, uint32_t k,
                                         float (&v)[8]) {
   unpack8(pk, v);
   if (p.prologue == ULLM_CUDA_PROLOGUE_SWIGLU) {  // the row is [gate(K) | up(K)]
-    float u[8];
-    unpack8(load8_packed<MODE>(p, m, p.k + k), u);
+    if (MODE != kModePushInCluster) {             // (never combined with the cluster gather)
+      float u[8];
+      unpack8(load8_packed<MODE>(p, m, p.k + k), u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = bf16_round_f32(v[i] / (1.0f + expf(-v[i])) * u[i]);
+      for (int i = 0; i < 8; ++i) v[i] = bf16_round_f32(v[i] / (1.0f + expf(-v[i])) * u[i]);
+    }
   } else if (p.prologue == ULLM_CUDA_PROLOGUE_RMSNORM) {
+    if (p.norm_weight != nullptr) {  // one rounding: bf16((x * inv) * gamma)
+      float g[8];
+      unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.norm_weight) + k), g);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = bf16_round_f32(v[i] * inv);
+      for (int i = 0; i < 8; ++i) v[i] = bf16_round_f32(v[i] * inv * g[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = bf16_round_f32(v[i] * inv);
+    }
   }
 }
 
@@ -310,20 +375,111 @@ __device__ __forceinline__ void emit_aq4(const Params &p, const Aq4Smem &s, uint
   }
 }
 
+// Cluster gather (consumer half of the fused all-reduce, one reading of the slots per cluster): block c of a
+// cluster of C blocks sums, for every row, the 16-byte units [c*per, (c+1)*per) of the ranks' slots (a unit =
+// two {value, tag} pairs), adds the residual, and stores the two bf16-rounded sums into the `gathered` array
+// of EVERY block of the cluster through distributed shared memory, together with its share of the sum of
+// squares.  After the cluster barrier every block holds all M rows as packed bf16 and the C partial sums of
+// squares (added in block order, so that all blocks compute the same RMSNorm factor).  The first cluster also
+// writes the fp32 sums to reduced_out.  Every thread of every block reaches the barrier whatever its waits did.
+template <int M, int T>
+__device__ void gather_cluster(const Params &p, uint32_t *gathered, float *ss_parts, float *red) {
+  const uint32_t C = cluster_nctarank(), cr = cluster_ctarank();
+  const uint32_t use_global = *p.pi.step_counter * p.pi.uses_per_step + p.pi.use;
+  const uint32_t want = use_global + 1u;
+  const uint8_t *base = p.pi.local_base + p.pi.slot_off[use_global & 1u];
+  const uint32_t units_row = p.k / 2;
+  const uint32_t per = (units_row + C - 1) / C;
+  const uint32_t u0 = cr * per;
+  const uint32_t u1 = u0 + per < units_row ? u0 + per : units_row;
+  const bool writer = cluster_id_x() == 0 && p.pi.reduced_out != nullptr;
+  const uint32_t g_addr = (uint32_t)__cvta_generic_to_shared(gathered);
+  const uint32_t s_addr = (uint32_t)__cvta_generic_to_shared(ss_parts);
+  float ss[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) ss[m] = 0.0f;
+  for (uint32_t i = threadIdx.x; i < (uint32_t)M * per; i += T) {
+    const uint32_t m = i / per, u = u0 + i % per;
+    if (u >= u1) continue;
+    const uint64_t e = (uint64_t)m * p.k + 2ull * u;  // first of the unit's two elements
+    float a = 0.0f, b = 0.0f;
+    if (p.pi.residual != nullptr) {
+      const float2 r = *reinterpret_cast<const float2 *>(p.pi.residual + e);
+      a = r.x, b = r.y;
+    }
+    const uint8_t *src = base + e * 8;
+    uint4 q[kMaxPeers];
+#pragma unroll
+    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r)
+      if (r < p.pi.tp)
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(q[r].x), "=r"(q[r].y), "=r"(q[r].z), "=r"(q[r].w)
+                     : "l"(src + (uint64_t)r * p.pi.slot_stride)
+                     : "memory");
+#pragma unroll
+    for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r)
+      if (r < p.pi.tp) {
+        if (q[r].y != want || q[r].w != want) {
+          uint4 one[1] = {q[r]};
+          poll_pairs<1>(p, reinterpret_cast<const uint4 *>(src + (uint64_t)r * p.pi.slot_stride), want, one);
+          q[r] = one[0];
+        }
+        a += __uint_as_float(q[r].x);
+        b += __uint_as_float(q[r].z);
+      }
+    if (writer) *reinterpret_cast<float2 *>(p.pi.reduced_out + e) = make_float2(a, b);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t w = *reinterpret_cast<const uint32_t *>(&h);
+    const float fa = __uint_as_float(w << 16), fb = __uint_as_float(w & 0xffff0000u);
+#pragma unroll
+    for (int mm = 0; mm < M; ++mm)
+      if ((uint32_t)mm == m) ss[mm] = fmaf(fa, fa, fmaf(fb, fb, ss[mm]));
+    const uint32_t dst = g_addr + (uint32_t)(e / 2) * 4u;
+    for (uint32_t c = 0; c < C; ++c) st_cluster_u32(map_to_block(dst, c), w);
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+    if ((threadIdx.x & 31) == 0) red[m * kMaxWarps + (threadIdx.x >> 5)] = ss[m];
+  }
+  __syncthreads();
+  if (threadIdx.x < (uint32_t)M) {
+    float t = 0.0f;
+    for (int w = 0; w < T / 32; ++w) t += red[threadIdx.x * kMaxWarps + w];
+    const uint32_t dst = s_addr + (threadIdx.x * kMaxClusterBlocks + cr) * 4u;
+    for (uint32_t c = 0; c < C; ++c) st_cluster_u32(map_to_block(dst, c), __float_as_uint(t));
+  }
+  cluster_sync_all();
+}
+
 // Stages prologue(x) for all M rows.  With RMSNorm the raw chunks are kept in registers
 // (packed bf16) between the sum-of-squares pass and the scaling pass whenever they fit, so x
 // is read from global memory once.
 template <int M, int T, int CACHE, uint32_t ENC, int MODE>
-__device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq, float *red) {
+__device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq, float *red, uint32_t *gathered,
+                                  float *ss_parts) {
   const uint32_t tid = threadIdx.x;
   const uint32_t nchunks = p.k / 8, padded = p.k_pad / 8;
   const bool rms = p.prologue == ULLM_CUDA_PROLOGUE_RMSNORM;
-  const bool cached = rms && nchunks <= (uint32_t)(CACHE * T);
-  uint4 cache[M][CACHE];
+  constexpr bool CLUSTER = MODE == kModePushInCluster;
+  const bool cached = !CLUSTER && rms && nchunks <= (uint32_t)(CACHE * T);
+  uint4 cache[M][CLUSTER ? 1 : CACHE];
   float inv[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) inv[m] = 1.0f;
-  if (rms) {
+  if (CLUSTER) {
+    gather_cluster<M, T>(p, gathered, ss_parts, red);
+    if (rms) {
+      const uint32_t C = cluster_nctarank();
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float t = 0.0f;
+        for (uint32_t c = 0; c < C; ++c) t += ss_parts[m * kMaxClusterBlocks + c];
+        inv[m] = 1.0f / sqrtf(t / (float)p.k + p.rms_eps);
+      }
+    }
+  } else if (rms) {
     float ss[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) ss[m] = 0.0f;
@@ -384,7 +540,7 @@ __device__ void stage_activations(const Params &p, float *xs, const Aq4Smem &aq,
     for (uint32_t c = tid; c < padded; c += T) {
 #pragma unroll
       for (int m = 0; m < M; ++m)
-        emit(c, m, c < nchunks ? load8_packed<MODE, (T <= 640)>(p, m, c * 8) : make_uint4(0u, 0u, 0u, 0u));
+        emit(c, m, c < nchunks ? load8_packed<MODE, (T <= 640)>(p, m, c * 8, gathered) : make_uint4(0u, 0u, 0u, 0u));
     }
   }
   __syncthreads();
@@ -409,6 +565,7 @@ __device__ __forceinline__ void store_out(const Params &p, uint32_t m, uint32_t 
                      : "memory");
     return;
   }
+  if (p.residual != nullptr) v += p.residual[(uint64_t)m * p.res_stride + col];
   if (p.y_dtype == ULLM_CUDA_DTYPE_F32)
     static_cast<float *>(p.y)[(uint64_t)m * p.y_stride + col] = v;
   else
@@ -417,19 +574,27 @@ __device__ __forceinline__ void store_out(const Params &p, uint32_t m, uint32_t 
 
 // M activation rows, R weight rows per warp pass, U 16-byte loads per row in flight, T threads.
 // With the SwiGLU epilogue (R even) a pass takes R/2 gate rows and the R/2 matching up rows.
-template <int M, int R, int U, uint32_t ENC, int T, int MODE>
+// S > 1: the K range of a row group is cut into S slices, taken by S consecutive warps of one block.
+template <int M, int R, int U, uint32_t ENC, int T, int MODE, int S = 1>
 __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  static_assert(S == 1 || (ENC == FP8 && (T / 32) % S == 0 && (T / 32) / S <= 15), "K slices: FP8 only, one named barrier per warp set");
   constexpr int E = Piece<ENC>::kElems;
   constexpr int CACHE = M <= 2 ? 4 : 2;
+  constexpr bool IN = MODE == kModePushIn || MODE == kModePushInCluster;
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t warp = threadIdx.x >> 5;
-  const uint32_t gwarp = blockIdx.x * (T / 32) + warp;
-  const uint32_t nwarps = gridDim.x * (T / 32);
+  // a warp set (S consecutive warps) works on one row group at a time
+  const uint32_t gwarp = (blockIdx.x * (T / 32) + warp) / S;
+  const uint32_t nwarps = gridDim.x * (T / 32) / S;
+  const uint32_t slice = S > 1 ? warp % S : 0u;
   const bool pair = p.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
   const uint32_t half_n = p.n / 2;
   const uint32_t groups = pair ? (half_n + R / 2 - 1) / (R / 2 > 0 ? R / 2 : 1) : (p.n + R - 1) / R;
   const uint32_t iters = p.k_pad / (E * 32);
+  const uint32_t it_per = (iters + S - 1) / S;
+  const uint32_t it_begin = slice * it_per;
+  const uint32_t it_end = it_begin + it_per < iters ? it_begin + it_per : iters;
   const uint32_t pieces = p.k_pad / 32;
   const uint64_t row_bytes = ENC == AQ4 ? p.k / 2 : p.k;
   // weight row of slot r in group g (>= n when out of range)
@@ -465,7 +630,7 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const uint32_t row = row_of(g, r);
-        if (it0 + u < iters && k0 < p.k && row < p.n)
+        if (it0 + u < it_end && k0 < p.k && row < p.n)
           wv[u][r] = ldg_stream(p.w + (uint64_t)row * row_bytes + (ENC == AQ4 ? k0 / 2 : k0));
         else
           wv[u][r] = make_uint4(0u, 0u, 0u, 0u);
@@ -476,14 +641,17 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   // Registers take the first step; the rest of the first group (up to 8 KiB per warp) is
   // pulled into L2 so that it is there when the activations have been staged.
   if (gwarp < groups) {
-    load_step(gwarp, 0);
+    load_step(gwarp, it_begin);
     if (lane < R) {
       const uint32_t row = row_of(gwarp, (int)lane);
-      uint32_t bytes = (uint32_t)row_bytes;
+      const uint32_t first = it_begin * (E * 32) / (ENC == AQ4 ? 2 : 1);  // byte offset of this warp's slice
+      uint32_t bytes = (uint32_t)row_bytes > first ? (uint32_t)row_bytes - first : 0u;
       const uint32_t cap = (8192u / R) & ~15u;
       bytes = bytes < cap ? bytes : cap;
+      if (S > 1) bytes = bytes < it_per * E * 32 ? bytes : it_per * E * 32;
+      bytes &= ~15u;
       if (row < p.n && bytes >= 16)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.w + (uint64_t)row * row_bytes), "r"(bytes)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.w + (uint64_t)row * row_bytes + first), "r"(bytes)
                      : "memory");
     }
   }
@@ -501,9 +669,15 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
     xs = reinterpret_cast<float *>(smem_raw);
     red = xs + (uint64_t)M * p.k_pad;
   }
-  stage_activations<M, T, CACHE, ENC, MODE>(p, xs, aq, red);
+  // after the block-reduction words: partial sums of the K slices, then the cluster gather's arrays
+  float *slice_part = red + M * kMaxWarps;                                  // [2][T/32][R*M] when S > 1
+  float *ss_parts = slice_part + (S > 1 ? 2 * (T / 32) * R * M : 0);        // [M][kMaxClusterBlocks]
+  uint32_t *gathered = reinterpret_cast<uint32_t *>(ss_parts + M * kMaxClusterBlocks);  // packed bf16 [M][K], 16-byte aligned
+  (void)IN;
+  stage_activations<M, T, CACHE, ENC, MODE>(p, xs, aq, red, gathered, ss_parts);
 
   bool prefetched = true;
+  uint32_t parity = 0;
   for (uint32_t g = gwarp; g < groups; g += nwarps) {
     float acc[R][M];
 #pragma unroll
@@ -511,12 +685,12 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
 #pragma unroll
       for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
 
-    for (uint32_t it0 = 0; it0 < iters; it0 += U) {
+    for (uint32_t it0 = it_begin; it0 < it_end; it0 += U) {
       if (!prefetched) load_step(g, it0);
       prefetched = false;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (it0 + u >= iters) break;
+        if (it0 + u >= it_end) break;
         const uint32_t it = it0 + u;
         if (ENC == FP8) {
           const float4 *xb = reinterpret_cast<const float4 *>(xs) + (it * 4) * 32 + lane;
@@ -610,7 +784,27 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         acc[r][m] = v;
       }
-    if (lane == 0) {
+    if (S > 1) {
+      // the S slices of this row group meet in shared memory; slice 0 adds them in slice order.  The buffers
+      // alternate, so a warp that runs ahead writes the other buffer and then stops at the next barrier.
+      float *mine = slice_part + ((uint64_t)parity * (T / 32) + warp) * (R * M);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int m = 0; m < M; ++m) mine[r * M + m] = acc[r][m];
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1u + warp / S), "n"(S * 32) : "memory");
+      if (slice == 0 && lane == 0) {
+        for (int sl = 1; sl < S; ++sl)
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[r][m] += mine[sl * (R * M) + r * M + m];
+      }
+      parity ^= 1u;
+    }
+    if (lane == 0 && slice == 0) {
       if (ENC == FP8) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -648,12 +842,16 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   }
 }
 
-inline size_t smem_bytes(uint32_t m, uint32_t k_pad, uint32_t enc) {
-  size_t bytes = (size_t)m * kMaxWarps * 4;
+// Shared memory of one block: staged activations, block-reduction words, K-slice partials (`slice_floats`)
+// and, for the cluster gather, the partial sums of squares and the gathered bf16 rows.
+inline size_t smem_bytes(uint32_t m, uint32_t k_pad, uint32_t enc, uint32_t k = 0, bool cluster = false,
+                         size_t slice_floats = 0) {
+  size_t bytes = (size_t)m * kMaxWarps * 4 + slice_floats * 4;
   if (enc == AQ4)
     bytes += (size_t)m * (k_pad / 32) * (24 * 4 + 4 + 4);
   else
     bytes += (size_t)m * k_pad * 4;
+  if (cluster) bytes += (size_t)m * kMaxClusterBlocks * 4 + (size_t)m * k * 2;
   return bytes;
 }
 
@@ -664,39 +862,119 @@ inline uint32_t pad_k(uint32_t k, uint32_t enc) {
   return (k + it - 1) / it * it;
 }
 
-template <int M, int R, int U, uint32_t ENC, int T>
-cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p) {
-  const size_t smem = smem_bytes(M, p.k_pad, ENC);
-  const int mode = p.pi.tp != 0 ? kModePushIn : (p.po.tp != 0 ? kModePushOut : kModePlain);
-  auto kern = mode == kModePushIn    ? matvec_kernel<M, R, U, ENC, T, kModePushIn>
-              : mode == kModePushOut ? matvec_kernel<M, R, U, ENC, T, kModePushOut>
-                                     : matvec_kernel<M, R, U, ENC, T, kModePlain>;
-  // The shared-memory attribute is raised once per (kernel, size); one CTA per SM by design.
+// Blocks per cluster for the cluster gather on this device: the largest of 8, 4, 2 whose co-resident clusters
+// keep at least 94 % of the blocks the best cluster size keeps (a larger cluster reads the ranks' slots fewer
+// times, but may leave SMs idle where a GPC's SM count is not a multiple of it).  0 = no cluster launch possible.
+template <typename Kern>
+int pick_cluster(Kern kern, int sm_count, int threads, size_t smem, int *blocks_out) {
+  int blocks_of[3] = {0, 0, 0};
+  const int sizes[3] = {8, 4, 2};
+  int most = 0;
+  for (int i = 0; i < 3; ++i) {
+    const int c = sizes[i];
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(sm_count / c * c));
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)c;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      continue;
+    }
+    int blocks = clusters * c;
+    if (blocks > sm_count / c * c) blocks = sm_count / c * c;
+    blocks_of[i] = blocks;
+    if (blocks > most) most = blocks;
+  }
+  for (int i = 0; i < 3; ++i)
+    if (blocks_of[i] > 0 && blocks_of[i] * 100 >= most * 94) {
+      *blocks_out = blocks_of[i];
+      return sizes[i];
+    }
+  *blocks_out = 0;
+  return 0;
+}
+
+template <int M, int R, int U, uint32_t ENC, int T, int S = 1>
+cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p_in) {
+  Params p = p_in;
+  const bool want_cluster = p.pi.tp != 0 && p.pi.cluster != 0;
+  constexpr size_t slice_floats = S > 1 ? (size_t)2 * (T / 32) * R * M : 0;
+  const int mode = p.pi.tp != 0 ? (want_cluster ? kModePushInCluster : kModePushIn) : (p.po.tp != 0 ? kModePushOut : kModePlain);
+  const size_t smem = smem_bytes(M, p.k_pad, ENC, p.k, mode == kModePushInCluster, slice_floats);
+  if (mode == kModePushInCluster && (smem > kSmemBudget || p.prologue == ULLM_CUDA_PROLOGUE_SWIGLU || p.k % 8 != 0)) {
+    p.pi.cluster = 0;  // the gathered rows do not fit beside the staged ones: every block gathers for itself
+    return launch_one<M, R, U, ENC, T, S>(ctx, stream, p);
+  }
+  auto kern = mode == kModePushIn           ? matvec_kernel<M, R, U, ENC, T, kModePushIn, S>
+              : mode == kModePushInCluster ? matvec_kernel<M, R, U, ENC, T, kModePushInCluster, S>
+              : mode == kModePushOut       ? matvec_kernel<M, R, U, ENC, T, kModePushOut, S>
+                                           : matvec_kernel<M, R, U, ENC, T, kModePlain, S>;
+  // Function attributes are per device: the shared-memory limit is raised once per (device, kernel, size) and the
+  // cluster shape is asked once per (device, kernel).  One block per SM by design.
   static std::mutex mu;
-  static size_t granted[3] = {0, 0, 0};
+  static size_t granted[kMaxDevices][4] = {};
+  static int cluster_size[kMaxDevices] = {}, cluster_blocks[kMaxDevices] = {};
+  const int dev = ctx->device;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  int csize = 0, cblocks = 0;
   {
     std::lock_guard<std::mutex> g(mu);
-    if (smem > granted[mode]) {
+    if (smem > granted[dev][mode]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
-      granted[mode] = smem;
+      granted[dev][mode] = smem;
+      if (mode == kModePushInCluster) cluster_size[dev] = 0;  // ask again with the new size
+    }
+    if (mode == kModePushInCluster) {
+      if (cluster_size[dev] == 0) {
+        cluster_size[dev] = pick_cluster(kern, ctx->sm_count, T, smem, &cluster_blocks[dev]);
+        if (cluster_size[dev] == 0) cluster_size[dev] = -1;
+      }
+      csize = cluster_size[dev];
+      cblocks = cluster_blocks[dev];
     }
   }
   const bool pair = p.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
   const uint32_t groups = pair ? (p.n / 2 + R / 2 - 1) / (R / 2 > 0 ? R / 2 : 1) : (p.n + R - 1) / R;
   uint32_t grid = (uint32_t)ctx->sm_count;
-  const uint32_t needed = (groups + (T / 32) - 1) / (T / 32);
+  const uint32_t sets = (T / 32) / S;  // warp sets per block
+  const uint32_t needed = (groups + sets - 1) / sets;
   if (grid > needed) grid = needed;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(T);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (mode == kModePushInCluster) {
+    if (csize < 2) {  // no cluster shape fits this device: every block gathers for itself
+      p.pi.cluster = 0;
+      return launch_one<M, R, U, ENC, T, S>(ctx, stream, p);
+    }
+    if (p.pi.cluster >= 2 && p.pi.cluster <= 8 && (p.pi.cluster & (p.pi.cluster - 1)) == 0 && (int)p.pi.cluster < csize)
+      csize = (int)p.pi.cluster;  // an explicitly smaller cluster was asked for
+    // whole clusters only, all of them co-resident: every block takes part in the gather whether or not it has rows
+    uint32_t blocks = (uint32_t)cblocks / (uint32_t)csize * (uint32_t)csize;
+    if (grid < blocks) blocks = (grid + (uint32_t)csize - 1) / (uint32_t)csize * (uint32_t)csize;
+    grid = blocks;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)csize;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.gridDim = dim3(grid);
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
@@ -706,8 +984,9 @@ inline double balance(uint32_t units, uint32_t warps) {
   return rounds == 0 ? 0.0 : (double)units / ((double)rounds * warps);
 }
 
-// Tuning override for measurements: ULLM_CUDA_MATVEC_VARIANT=<n> forces variant n of the M == 1
-// table below (read once).  -1 = choose by the balance rule.
+#ifdef ULLM_CUDA_TUNING
+// Tuning builds only (-DULLM_CUDA_TUNING): ULLM_CUDA_MATVEC_VARIANT=<n> forces variant n of the M == 1
+// table below (read once).  The shipped library reads no environment variable.
 inline int forced_variant() {
   static const int v = [] {
     const char *e = std::getenv("ULLM_CUDA_MATVEC_VARIANT");
@@ -715,6 +994,9 @@ inline int forced_variant() {
   }();
   return v;
 }
+#else
+inline int forced_variant() { return -1; }
+#endif
 
 template <uint32_t ENC>
 cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) {
@@ -730,6 +1012,13 @@ cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) 
     const double b1 = pair ? 0.0 : balance(rows, (uint32_t)ctx->sm_count * 32u);
     v = b2 >= b4 ? 8 : 9;
     if (b1 > (b2 > b4 ? b2 : b4) + 0.25) v = 4;  // few, long rows: one row per pass
+    if (ENC == FP8 && !pair && p.k >= 2048u) {
+      // Too few rows for one round of two-row groups over all warps (tensor-parallel shards): cut K four ways,
+      // so four times as many warps stream the weights.  One row per warp set when even that leaves warps idle.
+      const uint32_t warps = (uint32_t)ctx->sm_count * 32u;
+      const uint32_t units2 = (rows + 1) / 2;
+      if ((uint64_t)units2 * 10u < (uint64_t)warps * 7u) v = (uint64_t)units2 * 4u * 10u < (uint64_t)warps * 7u ? 14 : 18;
+    }
     if (ENC == AQ4) {
       // AQ4 holds more state per row (three integer accumulators): 1024 threads would spill.
       // Measured best: 4 rows x 2 loads (768 threads) for very tall matrices, else 2 rows x 4 loads.
@@ -737,14 +1026,15 @@ cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) 
     }
   }
   if (ENC == AQ4 && v != 0 && v != 2 && v != 11) v = 2;  // an unknown forced index falls back to a valid one
-  if (ENC == FP8 && v != 4 && v != 8 && v != 9) v = 8;
-  if (pair && v == 4) v = 8;  // the SwiGLU epilogue needs an even number of rows per pass
-  // three tuned configurations per encoding (forcing any other index is an error)
+  if (ENC == FP8 && v != 4 && v != 8 && v != 9 && v != 14 && v != 18) v = 8;
+  if (pair && (v == 4 || v == 14 || v == 18)) v = 8;  // the SwiGLU epilogue needs an even number of rows per pass
   if constexpr (ENC == FP8) {
     switch (v) {
       case 4: return launch_one<1, 1, 4, ENC, 1024>(ctx, stream, p);
       case 8: return launch_one<1, 2, 4, ENC, 1024>(ctx, stream, p);
       case 9: return launch_one<1, 4, 2, ENC, 640>(ctx, stream, p);
+      case 14: return launch_one<1, 1, 4, ENC, 1024, 4>(ctx, stream, p);
+      case 18: return launch_one<1, 2, 4, ENC, 1024, 4>(ctx, stream, p);
       default: return cudaErrorInvalidValue;
     }
   } else {

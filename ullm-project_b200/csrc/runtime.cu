@@ -7,11 +7,16 @@
 //   poll-with-deadline wait, timeout 0 = one poll  native/hip/src/hip_evidence_runtime.hip.cpp:508-535
 //   consume-once completion handles               native/hip/src/hip_evidence_runtime.hip.cpp:691-698
 //   exact-architecture check before any work      native/hip/src/hip_evidence_runtime.hip.cpp:463-496
+//   never free what is not proven complete; a background reaper with a bounded number of slots retires
+//   such resources, and new submissions are refused once a retirement stays unproven
+//                                                 native/hip/src/hip_evidence_runtime.hip.cpp:77-103, :151-257
 // There is no CPU fallback: without a usable sm_100 device every compute entry
 // answers ULLM_STATUS_CUDA_UNAVAILABLE (native/hip/src/hip_evidence_stub.cpp:103-127).
 #include "internal.hpp"
 
 #include <chrono>
+#include <condition_variable>
+#include <memory>
 #include <new>
 #include <thread>
 
@@ -111,6 +116,153 @@ ullm_status_t resolve_weight(const ullm_cuda_weight_t &w, const Context *ctx, si
   out->k = w.k;
   out->encoding = w.encoding;
   return ULLM_STATUS_OK;
+}
+
+
+// ---- retirement of resources whose completion is not yet proven ---------------------------------
+// A destructor never blocks on the device.  When the work that may still use a resource has not been
+// observed complete (cudaEventQuery / cudaStreamQuery), the resource is handed, together with a fence
+// event, to a background thread that polls the fence and releases the resource once it is reached.  A
+// fence that is not reached within kRetireDeadline is abandoned: the resource is leaked on purpose (the
+// process exit reclaims it) and the breaker opens, after which submissions are refused.  The number of
+// pending retirements is bounded; beyond it submissions are refused until the reaper catches up.
+namespace {
+
+constexpr size_t kMaxRetireSlots = 8;
+constexpr auto kRetireDeadline = std::chrono::seconds(120);
+
+struct Retired {
+  int device = 0;
+  cudaEvent_t fence = nullptr;            // recorded behind the last use
+  std::function<void()> release;          // frees the resources; runs with `device` current
+  std::chrono::steady_clock::time_point deadline;
+  Retired *next = nullptr;
+};
+
+class Reaper {
+ public:
+  bool start() noexcept {
+    std::lock_guard<std::mutex> g(m_);
+    if (started_) return true;
+    try {
+      std::thread(&Reaper::run, this).detach();  // never joined: process exit must not wait for the device
+      started_ = true;
+    } catch (...) {
+      started_ = false;
+    }
+    return started_;
+  }
+  // false: the breaker is open or every slot is taken
+  bool accepting() noexcept {
+    std::lock_guard<std::mutex> g(m_);
+    return !blocked_ && pending_ < kMaxRetireSlots;
+  }
+  bool blocked() noexcept {
+    std::lock_guard<std::mutex> g(m_);
+    return blocked_;
+  }
+  size_t pending() noexcept {
+    std::lock_guard<std::mutex> g(m_);
+    return pending_;
+  }
+  void enqueue(Retired *r) noexcept {
+    std::lock_guard<std::mutex> g(m_);
+    r->next = nullptr;
+    if (tail_ == nullptr) head_ = r; else tail_->next = r;
+    tail_ = r;
+    ++pending_;
+    cv_.notify_one();
+  }
+
+ private:
+  void run() noexcept {
+    for (;;) {
+      Retired *r = nullptr;
+      {
+        std::unique_lock<std::mutex> lk(m_);
+        cv_.wait(lk, [this] { return head_ != nullptr; });
+        r = head_;
+        head_ = r->next;
+        if (head_ == nullptr) tail_ = nullptr;
+      }
+      bool proven = false;
+      (void)cudaSetDevice(r->device);
+      for (;;) {
+        const cudaError_t e = cudaEventQuery(r->fence);
+        if (e == cudaSuccess) {
+          proven = true;
+          break;
+        }
+        if (e != cudaErrorNotReady) {
+          (void)cudaGetLastError();
+          break;  // the runtime is unhealthy: nothing is proven
+        }
+        if (std::chrono::steady_clock::now() >= r->deadline) break;
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      }
+      if (proven) {
+        try {
+          r->release();
+        } catch (...) {
+        }
+        (void)cudaEventDestroy(r->fence);
+        delete r;
+        std::lock_guard<std::mutex> g(m_);
+        --pending_;
+      } else {
+        // leaked on purpose: safety before reclamation
+        std::lock_guard<std::mutex> g(m_);
+        blocked_ = true;
+      }
+    }
+  }
+  std::mutex m_;
+  std::condition_variable cv_;
+  Retired *head_ = nullptr, *tail_ = nullptr;
+  size_t pending_ = 0;
+  bool started_ = false, blocked_ = false;
+};
+
+Reaper &reaper() {
+  static Reaper *r = new Reaper();  // leaked on purpose, like the registry
+  return *r;
+}
+
+}  // namespace
+
+bool submissions_open(sink_t *sink, ullm_status_t *status) noexcept {
+  if (reaper().accepting()) return true;
+  *status = write_error(sink, ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                        reaper().blocked() ? "an earlier retirement could not be proven complete; new submissions are refused"
+                                           : "too many resources are waiting to be retired; try again later");
+  return false;
+}
+
+// Releases `release` now when `stream` is observed idle, otherwise behind a fence on it.  Never blocks.
+// Returns false when the resources had to be abandoned (no fence could be made).
+bool retire_behind(int device, cudaStream_t stream, std::function<void()> release) noexcept {
+  (void)cudaSetDevice(device);
+  const cudaError_t q = cudaStreamQuery(stream);
+  if (q == cudaSuccess) {
+    release();
+    return true;
+  }
+  (void)cudaGetLastError();
+  Retired *r = new (std::nothrow) Retired();
+  cudaEvent_t ev = nullptr;
+  if (r == nullptr || !reaper().start() || cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventRecord(ev, stream) != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (ev != nullptr) (void)cudaEventDestroy(ev);
+    delete r;
+    return false;  // leaked: completion cannot be proven and nothing can watch for it
+  }
+  r->device = device;
+  r->fence = ev;
+  r->release = std::move(release);
+  r->deadline = std::chrono::steady_clock::now() + kRetireDeadline;
+  reaper().enqueue(r);
+  return true;
 }
 
 static cudaEvent_t take_event(Context *ctx, cudaError_t *err) {
@@ -283,7 +435,12 @@ ullm_status_t ullm_cuda_context_create(uint32_t device_ordinal, ullm_cuda_contex
     std::memset(c->host_flags, 0, 16 * sizeof(uint32_t));
     e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->device_flags), c->host_flags, 0);
   }
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&c->abort_word), 256);
+  if (e == cudaSuccess) e = cudaMemset(c->abort_word, 0, 256);
   if (e != cudaSuccess) {
+    if (c->host_flags) (void)cudaFreeHost(c->host_flags);
+    if (c->abort_word) (void)cudaFree(c->abort_word);
+    (void)cudaGetLastError();
     delete c;
     return cuda_error(sink, e, "context flag allocation");
   }
@@ -304,18 +461,33 @@ ullm_status_t ullm_cuda_context_destroy(ullm_cuda_context_t **context, ullm_cuda
   if (c->live_children.load() != 0)
     return errorf(sink, ULLM_STATUS_INVALID_ARGUMENT, "context still owns %llu queue/buffer/graph/comm/stack objects",
                   (unsigned long long)c->live_children.load());
+  // Every queue, buffer, graph, comm and stack of the context is gone (those still retiring behind a
+  // fence are counted as live), so no work of this context can be in flight: nothing to wait for.
   registry().remove(c);
   (void)cudaSetDevice(c->device);
-  (void)cudaDeviceSynchronize();
   for (cudaEvent_t ev : c->event_pool) (void)cudaEventDestroy(ev);
   (void)cudaFreeHost(c->host_flags);
-  if (c->scratch != nullptr) (void)cudaFree(c->scratch);
-  if (c->tile_counters != nullptr) (void)cudaFree(c->tile_counters);
+  (void)cudaFree(c->abort_word);
   c->magic = 0;
   delete c;
   *context = nullptr;
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("context destroy")
+}
+
+ullm_status_t ullm_cuda_context_set_wait_limit(ullm_cuda_context_t *context, uint32_t limit_ms,
+                                               ullm_cuda_error_sink_t *error_sink) {
+  ULLM_ENTRY_BEGIN
+  sink_t *sink = error_sink;
+  ullm_status_t st = validate_sink(sink);
+  if (st != ULLM_STATUS_OK) return st;
+  Context *c = as_context(context);
+  if (c == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "context handle is not live");
+  if (limit_ms == 0 || limit_ms > 600000U)
+    return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "the wait limit must be between 1 ms and 600000 ms");
+  c->wait_limit_ms.store(limit_ms);
+  return ULLM_STATUS_OK;
+  ULLM_ENTRY_END("context set wait limit")
 }
 
 ullm_status_t ullm_cuda_queue_create(ullm_cuda_context_t *context, ullm_cuda_queue_t **queue,
@@ -340,6 +512,10 @@ ullm_status_t ullm_cuda_queue_create(ullm_cuda_context_t *context, ullm_cuda_que
     return cuda_error(sink, e, "queue create");
   }
   c->live_children++;
+  {
+    std::lock_guard<std::mutex> g(c->mutex);
+    c->queues.push_back(q);
+  }
   registry().add(q);
   *queue = reinterpret_cast<ullm_cuda_queue_t *>(q);
   return ULLM_STATUS_OK;
@@ -354,15 +530,33 @@ ullm_status_t ullm_cuda_queue_destroy(ullm_cuda_queue_t **queue, ullm_cuda_error
   if (queue == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "queue pointer is null");
   Queue *q = as_queue(*queue);
   if (q == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "queue handle is not live");
+  if (q->capturing) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "queue is still capturing");
   registry().remove(q);
-  (void)cudaSetDevice(q->ctx->device);
-  (void)cudaStreamSynchronize(q->stream);
-  (void)cudaStreamDestroy(q->stream);
-  (void)cudaFreeHost(q->staging);
-  q->ctx->live_children--;
+  Context *ctx = q->ctx;
   q->magic = 0;
-  delete q;
+  // The handle is dead from here on; the stream, its pinned staging and the GEMM scratch are released
+  // as soon as the stream is observed idle (at once when it already is), never by blocking the caller.
+  // Until then the stream stays on the context's list, so that a buffer freed meanwhile still waits for it.
+  const bool watched = retire_behind(ctx->device, q->stream, [q, ctx] {
+    {
+      std::lock_guard<std::mutex> g(ctx->mutex);
+      for (size_t i = 0; i < ctx->queues.size(); ++i)
+        if (ctx->queues[i] == q) {
+          ctx->queues.erase(ctx->queues.begin() + static_cast<long>(i));
+          break;
+        }
+    }
+    (void)cudaStreamDestroy(q->stream);
+    (void)cudaFreeHost(q->staging);
+    if (q->scratch.ptr != nullptr) (void)cudaFree(q->scratch.ptr);
+    if (q->scratch.tile_counters != nullptr) (void)cudaFree(q->scratch.tile_counters);
+    ctx->live_children--;
+    delete q;
+  });
   *queue = nullptr;
+  if (!watched)
+    return write_error(sink, ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                       "queue retired without proof of completion: its resources are abandoned, not freed");
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("queue destroy")
 }
@@ -405,14 +599,37 @@ ullm_status_t ullm_cuda_buffer_free(ullm_cuda_buffer_t **buffer, ullm_cuda_error
   Buffer *b = as_buffer(*buffer);
   if (b == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "buffer handle is not live");
   registry().remove(b);
-  (void)cudaSetDevice(b->ctx->device);
-  // cudaFree synchronises the device, so no queued kernel can still be using the memory.
-  cudaError_t e = cudaFree(b->ptr);
-  b->ctx->live_children--;
+  Context *ctx = b->ctx;
   b->magic = 0;
-  delete b;
   *buffer = nullptr;
-  if (e != cudaSuccess) return cuda_error(sink, e, "cudaFree");
+  // Any queue of the context may still have work that uses the memory.  It is freed at once when every
+  // queue is observed idle; otherwise the free waits, in the background, behind a fence on each busy queue.
+  std::vector<cudaStream_t> busy;
+  (void)cudaSetDevice(ctx->device);
+  {
+    std::lock_guard<std::mutex> g(ctx->mutex);
+    for (Queue *q : ctx->queues)
+      if (cudaStreamQuery(q->stream) != cudaSuccess) busy.push_back(q->stream);
+  }
+  (void)cudaGetLastError();
+  auto remaining = std::make_shared<std::atomic<size_t>>(busy.size());
+  auto release = [b, ctx] {
+    (void)cudaFree(b->ptr);
+    ctx->live_children--;
+    delete b;
+  };
+  if (busy.empty()) {
+    release();
+    return ULLM_STATUS_OK;
+  }
+  bool watched = true;
+  for (cudaStream_t s : busy)
+    watched = retire_behind(ctx->device, s, [remaining, release] {
+                if (remaining->fetch_sub(1) == 1) release();
+              }) && watched;
+  if (!watched)
+    return write_error(sink, ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                       "buffer retired without proof of completion: its memory is abandoned, not freed");
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("buffer free")
 }
@@ -520,6 +737,7 @@ ullm_status_t ullm_cuda_queue_signal(ullm_cuda_queue_t *queue, ullm_cuda_complet
   st = begin_op(queue, sink, &q);
   if (st != ULLM_STATUS_OK) return st;
   if (q->capturing) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "cannot signal while capturing");
+  if (!submissions_open(sink, &st)) return st;
   cudaError_t e = cudaSuccess;
   cudaEvent_t ev = take_event(q->ctx, &e);
   if (e != cudaSuccess) return cuda_error(sink, e, "cudaEventCreate");
@@ -534,6 +752,8 @@ ullm_status_t ullm_cuda_queue_signal(ullm_cuda_queue_t *queue, ullm_cuda_complet
     return write_error(sink, ULLM_STATUS_INTERNAL_ERROR, "host allocation failed");
   }
   c->queue = q;
+  c->ctx = q->ctx;
+  c->stream = q->stream;
   c->event = ev;
   {
     std::lock_guard<std::mutex> g(q->mutex);
@@ -554,10 +774,16 @@ static Completion *as_completion(const ullm_cuda_completion_t *h) {
   return (c && c->magic == kMagicCompletion) ? c : nullptr;
 }
 
-static void retire_completion(Completion *c) {
+// The handle dies here.  Its event returns to the pool only when it has been observed reached; an event
+// that may still be pending is destroyed instead (the runtime defers that until it completes), so that
+// no later completion can be confused with this one.
+static void retire_completion(Completion *c, bool reached) {
   registry().remove(c);
-  give_event(c->queue->ctx, c->event);
-  c->queue->ctx->live_children--;
+  if (reached)
+    give_event(c->ctx, c->event);
+  else
+    (void)cudaEventDestroy(c->event);
+  c->ctx->live_children--;
   c->magic = 0;
   delete c;
 }
@@ -570,7 +796,7 @@ ullm_status_t ullm_cuda_completion_query(ullm_cuda_completion_t *completion, uin
   if (st != ULLM_STATUS_OK) return st;
   Completion *c = as_completion(completion);
   if (c == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "completion handle is not live");
-  (void)cudaSetDevice(c->queue->ctx->device);
+  (void)cudaSetDevice(c->ctx->device);
   bool reached = false;
   cudaError_t e = poll_event(c->event, timeout_ms, &reached);
   if (e != cudaSuccess) return cuda_error(sink, e, "cudaEventQuery");
@@ -592,15 +818,21 @@ ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint
   }
   Completion *c = as_completion(completion);
   if (c == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "completion handle is not live");
-  Context *ctx = c->queue->ctx;
+  Context *ctx = c->ctx;
+  const Queue *c_queue = c->queue;
   (void)cudaSetDevice(ctx->device);
   bool reached = false;
   cudaError_t e = poll_event(c->event, timeout_ms, &reached);
+  // Like the reference (hip_evidence_runtime.hip.cpp:691-716) the handle is consumed by EVERY outcome,
+  // a timeout included: a caller cannot retry a wait.  Polling without consuming is ullm_cuda_completion_query.
   if (e != cudaSuccess) {
-    retire_completion(c);
+    retire_completion(c, false);
     return cuda_error(sink, e, "cudaEventQuery");
   }
-  if (!reached) return write_error(sink, ULLM_STATUS_CUDA_TIMEOUT, "completion not reached before the deadline");
+  if (!reached) {
+    retire_completion(c, false);
+    return write_error(sink, ULLM_STATUS_CUDA_TIMEOUT, "completion not reached before the deadline; the handle is consumed");
+  }
   uint32_t flags[16];
   uint32_t any = 0;
   for (int i = 0; i < 16; ++i) {
@@ -615,9 +847,15 @@ ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint
     result->terminal = 1U;
     result->device_flags = any;
   }
-  retire_completion(c);
+  cudaStream_t stream = c->stream;
+  retire_completion(c, true);
   if (any != 0U) {
     for (int i = 0; i < 16; ++i) const_cast<volatile uint32_t *>(ctx->host_flags)[i] = 0U;
+    // re-arm the device-side abort word behind the work that tripped it (the queue may be gone by now)
+    if (as_queue(reinterpret_cast<const ullm_cuda_queue_t *>(c_queue)) != nullptr)
+      (void)cudaMemsetAsync(ctx->abort_word, 0, sizeof(uint32_t), stream);
+    else
+      (void)cudaMemset(ctx->abort_word, 0, sizeof(uint32_t));
     return errorf(sink, ULLM_STATUS_CUDA_DEVICE_FLAGGED,
                   "a kernel gave up a bounded wait (flags %08x %08x %08x %08x); results are not valid", flags[0],
                   flags[1], flags[2], flags[3]);
@@ -636,7 +874,7 @@ ullm_status_t ullm_cuda_completion_elapsed_ms(ullm_cuda_completion_t *start, ull
   if (a == nullptr || b == nullptr)
     return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "completion handle is not live");
   if (milliseconds == nullptr) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "output is null");
-  (void)cudaSetDevice(a->queue->ctx->device);
+  (void)cudaSetDevice(a->ctx->device);
   cudaError_t e = cudaEventElapsedTime(milliseconds, a->event, b->event);
   if (e == cudaErrorNotReady) {
     (void)cudaGetLastError();
@@ -660,8 +898,9 @@ ullm_status_t ullm_cuda_completion_destroy(ullm_cuda_completion_t **completion,
     *completion = nullptr;  // consumed by a successful wait: destroying it again is harmless
     return ULLM_STATUS_OK;
   }
-  // The event returns to the pool; a pending event is simply re-recorded by its next user.
-  retire_completion(c);
+  (void)cudaSetDevice(c->ctx->device);
+  retire_completion(c, cudaEventQuery(c->event) == cudaSuccess);
+  (void)cudaGetLastError();
   *completion = nullptr;
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("completion destroy")
@@ -765,7 +1004,7 @@ ullm_status_t ullm_cuda_graph_destroy(ullm_cuda_graph_t **graph, ullm_cuda_error
     return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "graph handle is not live");
   registry().remove(g);
   (void)cudaSetDevice(g->ctx->device);
-  (void)cudaDeviceSynchronize();
+  // destroying an executable graph that is still running is legal: the runtime keeps what the launch needs
   (void)cudaGraphExecDestroy(g->exec);
   (void)cudaGraphDestroy(g->graph);
   g->ctx->live_children--;

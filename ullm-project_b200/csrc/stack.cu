@@ -5,21 +5,28 @@
 // (docs/plans/main-plan.md:55).  What it fixes is the shape of the boundary: work is
 // enqueued on a queue and observed through a completion (docs/architecture/runtime.md:77-79).
 //
-// Dataflow of one step (no attention is computed; the glue is the minimum that keeps
-// the shapes chained and the magnitudes stable):
-//   h          = input bf16 [m, hidden]
-//   qkv        = QKV( rmsnorm(h) )                      column-parallel, bf16 out
-//   o          = O( qkv[:, :q_local] )                  row-parallel, fp32 out, sum over ranks
-//   act        = swiglu( GateUp( rmsnorm(o) ) )         column-parallel rows [gate_l | up_l], bf16 out [m, ffn/tp]
-//   h          = Down( act )                            row-parallel, fp32 out, sum over ranks
-//   logits     = LMHead( rmsnorm(h) )                   column-parallel, bf16 out [m, vocab/tp]
-// rmsnorm runs inside the consuming kernel's activation staging, swiglu in the
-// producing kernel's epilogue.
+// Dataflow of one step: the projections of a decoder block with their glue (no attention is computed;
+// the first semantic ops the reference plans after its skeleton are exactly these:
+// docs/plans/archive/2026/08/1-10/phase2-h3-g0-model-free-gpu.md:42):
+//   h          = f32( input bf16 [m, hidden] )          the residual stream, fp32
+//   qkv        = QKV( rmsnorm(bf16 h, g1) )             column-parallel, bf16 out
+//   h          = h + O( qkv[:, :q_local] )              row-parallel, sum over ranks, residual add
+//   act        = swiglu( GateUp( rmsnorm(bf16 h, g2) ) ) column-parallel rows [gate_l | up_l], bf16 out [m, ffn/tp]
+//   h          = h + Down( act )                        row-parallel, sum over ranks, residual add
+//   logits     = LMHead( rmsnorm(bf16 h, gf) )          column-parallel, bf16 out [m, vocab/tp]
+// rmsnorm (with its weight vector) runs inside the consuming kernel's activation staging, swiglu in the
+// producing kernel's epilogue, and the residual add either in the row-parallel kernel's epilogue (one GPU,
+// or before an NCCL all-reduce on rank 0) or, with the fused all-reduce, in the consuming kernel's staging:
+// "sum over ranks + residual + norm" is then one pass over the ranks' slots.
+// h alternates between two fp32 buffers (a linear never updates its own residual in place: the blocks of a
+// kernel read it while one of them writes the new value).
 //
 // Weights are generated on the device from (seed, tensor id, element index) and
 // quantised there.  FP8 row-parallel shards are cut out of rows quantised over the
 // FULL K, so that every tensor-parallel degree uses the same codes and scales.
 #include "internal.hpp"
+
+#include <cuda_bf16.h>
 
 #include <chrono>
 #include <cstdlib>
@@ -42,7 +49,11 @@ struct StackLinear {
   uint32_t prologue = 0, epilogue = 0, x_dtype = 0, y_dtype = 0;
   uint64_t in_off = 0, out_off = 0;  // into the activation buffer
   uint64_t x_stride = 0, y_stride = 0;
-  bool in_is_step_input = false, out_is_step_output = false;
+  bool out_is_step_output = false;
+  bool has_norm = false, has_residual = false;
+  uint64_t norm_off = 0;       // bf16 gamma[K] in the weight buffer
+  uint64_t norm_tensor_id = 0;
+  uint64_t res_off = 0;        // fp32 residual [m, hidden] in the activation buffer (row-parallel linears)
 };
 
 }  // namespace
@@ -51,6 +62,7 @@ struct Stack {
   uint32_t magic = kMagicStack;
   Context *ctx = nullptr;
   Queue *queue = nullptr;
+  cudaStream_t stream = nullptr;  // the queue's, kept so that destruction does not touch a queue handle that died first
   Comm *comm = nullptr;
   ullm_cuda_stack_desc_t desc{};
   std::vector<StackLinear> linears;
@@ -71,13 +83,27 @@ struct Stack {
   uint64_t step_counter_off = 0;        // local word bumped once per step
   uint64_t slot_stride = 0;
   uint32_t sites = 0;                   // row-parallel linears per step
+  uint32_t gather_cluster = 0;          // non-zero: consumers gather the ranks' slots once per cluster
+  uint64_t h0_off = 0;                  // fp32 copy of the step input (the residual stream's first value)
 };
 
 namespace {
 
 uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-__global__ void step_tick_kernel(uint32_t *counter) { *counter += 1u; }
+// First kernel of every step: the bf16 input becomes the fp32 residual stream, and (fused all-reduce) the step
+// counter every tag of the step derives from is bumped.
+__global__ void step_begin_kernel(const __nv_bfloat16 *in, float *h, uint64_t count, uint32_t *counter) {
+  if (counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *counter += 1u;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x)
+    h[i] = __bfloat162float(in[i]);
+}
+
+// gamma[i] = bf16(1 + z(seed, tensor, i) / 8), z the same counter-based normal stream the weights use
+__global__ void gamma_kernel(const float *z, __nv_bfloat16 *out, uint64_t count) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(1.0f + z[i] * 0.125f);
+}
 
 uint64_t values_bytes(uint32_t enc, uint64_t n, uint64_t k) { return enc == ULLM_CUDA_ENCODING_AQ4 ? n * (k / 2) : n * k; }
 uint64_t scales_bytes(uint32_t enc, uint64_t n, uint64_t k) {
@@ -100,15 +126,6 @@ Buffer *make_buffer(Context *ctx, uint64_t bytes, cudaError_t *err) {
   ctx->live_children++;
   registry().add(b);
   return b;
-}
-
-void drop_buffer(Buffer *b) {
-  if (b == nullptr) return;
-  registry().remove(b);
-  (void)cudaFree(b->ptr);
-  b->ctx->live_children--;
-  b->magic = 0;
-  delete b;
 }
 
 // Copies columns [c0, c0+cols) of a row-major [rows, full_cols] byte matrix.
@@ -163,7 +180,7 @@ LinearArgs make_args(const Stack *st, const StackLinear &L, uint32_t m) {
   uint8_t *iobase = static_cast<uint8_t *>(st->io->ptr);
   a.w = wbase + L.values_off;
   a.scales = wbase + L.scales_off;
-  a.x = L.in_is_step_input ? iobase : abase + L.in_off;
+  a.x = abase + L.in_off;
   a.y = L.out_is_step_output ? iobase + st->io_out_off : abase + L.out_off;
   a.m = m;
   a.n = static_cast<uint32_t>(L.n);
@@ -176,7 +193,24 @@ LinearArgs make_args(const Stack *st, const StackLinear &L, uint32_t m) {
   a.prologue = L.prologue;
   a.epilogue = L.epilogue;
   a.rms_eps = st->desc.rms_eps;
+  a.norm_weight = L.has_norm ? wbase + L.norm_off : nullptr;
+  a.residual = L.has_residual ? reinterpret_cast<const float *>(abase + L.res_off) : nullptr;
+  a.res_stride = L.y_stride;
+  a.wait_limit_ms = st->ctx->wait_limit_ms.load();
+  a.abort_word = st->ctx->abort_word;
   return a;
+}
+
+// The fused all-reduce lives in the matvec kernels: a step uses it only when every linear of the step is served
+// by them at this token count (otherwise the whole step sums with NCCL, the same verdict on every rank, which
+// all build the same shapes).
+bool step_can_push(const Stack *st, uint32_t m) {
+  if (!st->push || m > 8) return false;
+  for (const StackLinear &L : st->linears) {
+    const char *why = "";
+    if (!matvec_supports(make_args(st, L, m), &why)) return false;
+  }
+  return true;
 }
 
 // Enqueues every kernel of one step on the stack's stream; returns launches or -1.
@@ -184,21 +218,30 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
   cudaStream_t s = st->queue->stream;
   int64_t launches = 0;
   const uint32_t tp = st->desc.tp_size;
-  const bool push = st->push && m <= 8;  // the matvec path carries the fused all-reduce
-  if (push) {
-    // one tick per step: every tag of this step derives from the counter
-    step_tick_kernel<<<1, 1, 0, s>>>(reinterpret_cast<uint32_t *>(comm_sym_ptr(st->comm, st->desc.tp_rank) + st->step_counter_off));
+  const bool push = step_can_push(st, m);
+  {
+    uint8_t *abase = static_cast<uint8_t *>(st->acts->ptr);
+    const uint64_t count = (uint64_t)m * st->desc.hidden;
+    uint32_t *counter = push ? reinterpret_cast<uint32_t *>(comm_sym_ptr(st->comm, st->desc.tp_rank) + st->step_counter_off) : nullptr;
+    const unsigned blocks = (unsigned)((count + 1023) / 1024 > 64 ? 64 : (count + 1023) / 1024);
+    step_begin_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(st->io->ptr),
+                                             reinterpret_cast<float *>(abase + st->h0_off), count, counter);
     *err = cudaGetLastError();
     if (*err != cudaSuccess) {
-      if (why) *why = "step tick launch failed";
+      if (why) *why = "step begin launch failed";
       return -1;
     }
     ++launches;
   }
   uint32_t site = 0;                      // row-parallel linears seen so far in this step
   bool consume = false;                   // the previous linear pushed: this one sums the slots
+  const float *pending_residual = nullptr;  // ... and adds the residual the pushing linear left to it
+  float *pending_out = nullptr;
   for (const StackLinear &L : st->linears) {
     LinearArgs a = make_args(st, L, m);
+    // with several ranks the residual enters the sum exactly once: on rank 0 before an NCCL all-reduce, in the
+    // consumer's staging with the fused all-reduce
+    if (L.row_parallel && tp > 1 && (push || st->desc.tp_rank != 0)) a.residual = nullptr;
     if (push && (consume || L.row_parallel)) {
       uint8_t *local = comm_sym_ptr(st->comm, st->desc.tp_rank);
       const uint32_t *counter = reinterpret_cast<const uint32_t *>(local + st->step_counter_off);
@@ -212,8 +255,10 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
         a.push_in.step_counter = counter;
         a.push_in.uses_per_step = uses_of(r);
         a.push_in.use = (site - 1) / Stack::kRing;
-        a.push_in.reduced_out = const_cast<float *>(static_cast<const float *>(a.x));  // keeps the sum readable
+        a.push_in.residual = pending_residual;
+        a.push_in.reduced_out = pending_out;  // keeps residual + sum: the next residual, and readable by tests
         a.push_in.tp = tp;
+        a.push_in.cluster = st->gather_cluster;
       }
       if (L.row_parallel) {
         const uint32_t r = site % Stack::kRing;
@@ -226,6 +271,9 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
         a.push_out.use = site / Stack::kRing;
         a.push_out.tp = tp;
         a.push_out.rank = st->desc.tp_rank;
+        uint8_t *abase = static_cast<uint8_t *>(st->acts->ptr);
+        pending_residual = L.has_residual ? reinterpret_cast<const float *>(abase + L.res_off) : nullptr;
+        pending_out = reinterpret_cast<float *>(abase + L.out_off);
       }
     }
     consume = push && L.row_parallel;
@@ -235,10 +283,10 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
     // the fused all-reduce lives in the matvec kernels; without it the faster kernel for the token count runs
     const char *reason_gemm = "";
     const bool mv = matvec_supports(a, &reason);
-    if (mv && (push || !(gemm_supports(st->ctx, a, &reason_gemm) && auto_prefers_gemm(a)))) {
+    if (mv && (push || !(gemm_supports(a, &reason_gemm) && auto_prefers_gemm(a)))) {
       n = launch_matvec(st->ctx, s, a, err);
-    } else if (gemm_supports(st->ctx, a, &reason)) {
-      n = launch_gemm(st->ctx, s, a, err);
+    } else if (gemm_supports(a, &reason)) {
+      n = launch_gemm(st->ctx, &st->queue->scratch, s, a, err);
     } else {
       *err = cudaErrorNotSupported;
       if (why) *why = std::string("no kernel serves a stack linear: ") + reason;
@@ -249,10 +297,7 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
       return -1;
     }
     launches += n;
-    // Measurement aid: ULLM_CUDA_DEBUG_SKIP_REDUCE=1 leaves the partial sums unreduced (WRONG
-    // results) so that a step can be timed without any communication.
-    static const bool skip_reduce = std::getenv("ULLM_CUDA_DEBUG_SKIP_REDUCE") != nullptr;
-    if (L.row_parallel && st->desc.tp_size > 1 && !push && !skip_reduce) {
+    if (L.row_parallel && tp > 1 && !push) {
       std::string nccl_why;
       *err = comm_all_reduce_raw(st->comm, s, a.y, static_cast<uint64_t>(m) * L.y_stride, ULLM_CUDA_DTYPE_F32, &nccl_why);
       if (*err != cudaSuccess) {
@@ -267,6 +312,10 @@ int64_t enqueue_step(Stack *st, uint32_t m, cudaError_t *err, std::string *why) 
 }
 
 ullm_status_t run_step(Stack *st, uint32_t m, sink_t *sink) {
+  ullm_status_t refused = ULLM_STATUS_OK;
+  if (!submissions_open(sink, &refused)) return refused;
+  if (as_queue(reinterpret_cast<const ullm_cuda_queue_t *>(st->queue)) == nullptr)
+    return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "the stack's queue has been destroyed");
   cudaStream_t s = st->queue->stream;
   cudaError_t e = cudaSuccess;
   std::string why;
@@ -313,19 +362,35 @@ Stack *as_stack(const ullm_cuda_stack_t *h) {
   return (s && s->magic == kMagicStack) ? s : nullptr;
 }
 
-void destroy_stack(Stack *st) {
+// Never blocks: graphs may be destroyed while they run, everything a running step may still touch (weights,
+// activations, pinned staging) is released once the queue's last work is observed complete.  `counted` = the
+// stack was registered as a child of its context.
+bool destroy_stack(Stack *st, bool counted) {
   (void)cudaSetDevice(st->ctx->device);
-  (void)cudaStreamSynchronize(st->queue->stream);
   for (auto &kv : st->graphs) (void)cudaGraphExecDestroy(kv.second);
   for (auto &kv : st->graph_defs) (void)cudaGraphDestroy(kv.second);
-  if (st->done) (void)cudaEventDestroy(st->done);
-  if (st->pinned_in) (void)cudaFreeHost(st->pinned_in);
-  if (st->pinned_out) (void)cudaFreeHost(st->pinned_out);
-  drop_buffer(st->weights);
-  drop_buffer(st->acts);
-  drop_buffer(st->io);
+  st->graphs.clear();
+  st->graph_defs.clear();
   st->magic = 0;
-  delete st;
+  if (st->comm != nullptr && st->push && as_comm(reinterpret_cast<const ullm_cuda_comm_t *>(st->comm)) != nullptr)
+    comm_sym_release(st->comm);
+  for (Buffer *b : {st->weights, st->acts, st->io})
+    if (b != nullptr) registry().remove(b);  // the spans handed out by linear_info die with the stack
+  Context *ctx = st->ctx;
+  return retire_behind(ctx->device, st->stream, [st, ctx, counted] {
+    if (st->done) (void)cudaEventDestroy(st->done);
+    if (st->pinned_in) (void)cudaFreeHost(st->pinned_in);
+    if (st->pinned_out) (void)cudaFreeHost(st->pinned_out);
+    for (Buffer *b : {st->weights, st->acts, st->io})
+      if (b != nullptr) {
+        (void)cudaFree(b->ptr);
+        ctx->live_children--;
+        b->magic = 0;
+        delete b;
+      }
+    if (counted) ctx->live_children--;
+    delete st;
+  });
 }
 
 }  // namespace
@@ -382,6 +447,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   if (S == nullptr) return write_error(sink, ULLM_STATUS_INTERNAL_ERROR, "host allocation failed");
   S->ctx = ctx;
   S->queue = q;
+  S->stream = q->stream;
   S->comm = cm;
   S->desc = d;
   if (!(S->desc.rms_eps > 0.0f)) S->desc.rms_eps = 1e-5f;
@@ -395,15 +461,16 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     aoff = align_up(aoff + bytes, 256);
     return o;
   };
+  S->h0_off = take_act(mt * d.hidden * 4);
   // One set of activation spans shared by all layers, or one set per layer when the
   // caller wants to read every intermediate back (parity checks).
   const uint32_t act_sets = (d.flags & ULLM_CUDA_STACK_FLAG_KEEP_ACTIVATIONS) ? d.layers : 1;
-  std::vector<uint64_t> act_qkv_v(act_sets), act_o_v(act_sets), act_gu_v(act_sets), act_h_v(act_sets);
+  std::vector<uint64_t> act_qkv_v(act_sets), act_h1_v(act_sets), act_gu_v(act_sets), act_h2_v(act_sets);
   for (uint32_t i = 0; i < act_sets; ++i) {
     act_qkv_v[i] = take_act(mt * nq * 2);
-    act_o_v[i] = take_act(mt * d.hidden * 4);
+    act_h1_v[i] = take_act(mt * d.hidden * 4);  // h after the attention output projection
     act_gu_v[i] = take_act(mt * fl * 2);
-    act_h_v[i] = take_act(mt * d.hidden * 4);
+    act_h2_v[i] = take_act(mt * d.hidden * 4);  // h after the MLP
   }
   uint64_t woff = 0;
   auto add = [&](uint32_t layer, uint32_t which, uint64_t full_n, uint64_t full_k, uint64_t n, uint64_t k,
@@ -423,20 +490,25 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     woff = align_up(woff + values_bytes(d.encoding, n, k), 256);
     L.scales_off = woff;
     woff = align_up(woff + scales_bytes(d.encoding, n, k), 256);
+    if (!row_parallel) {  // the column-parallel linears start with an RMSNorm: its weight vector
+      L.has_norm = true;
+      L.norm_tensor_id = (uint64_t(layer) << 8) | which | (2ull << 40);
+      L.norm_off = woff;
+      woff = align_up(woff + k * 2, 256);
+    }
     S->weight_bytes += values_bytes(d.encoding, n, k) + scales_bytes(d.encoding, n, k);
     S->linears.push_back(L);
     return S->linears.back();
   };
   for (uint32_t l = 0; l < d.layers; ++l) {
     const uint32_t si = act_sets == 1 ? 0 : l, sp = act_sets == 1 ? 0 : (l == 0 ? 0 : l - 1);
-    const uint64_t act_qkv = act_qkv_v[si], act_o = act_o_v[si], act_gu = act_gu_v[si], act_h = act_h_v[si];
-    const uint64_t act_h_prev = act_h_v[sp];
+    const uint64_t act_qkv = act_qkv_v[si], act_h1 = act_h1_v[si], act_gu = act_gu_v[si], act_h2 = act_h2_v[si];
+    const uint64_t h_prev = l == 0 ? S->h0_off : act_h2_v[sp];
     {
       StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_QKV, qd + 2 * kvd, d.hidden, nq, d.hidden, d.tp_rank * ql, 0, false);
       L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
-      L.in_is_step_input = l == 0;
-      L.in_off = act_h_prev;
-      L.x_dtype = l == 0 ? ULLM_CUDA_DTYPE_BF16 : ULLM_CUDA_DTYPE_F32;
+      L.in_off = h_prev;
+      L.x_dtype = ULLM_CUDA_DTYPE_F32;
       L.x_stride = d.hidden;
       L.out_off = act_qkv;
       L.y_dtype = ULLM_CUDA_DTYPE_BF16;
@@ -448,7 +520,9 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
       L.in_off = act_qkv;
       L.x_dtype = ULLM_CUDA_DTYPE_BF16;
       L.x_stride = nq;
-      L.out_off = act_o;
+      L.has_residual = true;
+      L.res_off = h_prev;
+      L.out_off = act_h1;
       L.y_dtype = ULLM_CUDA_DTYPE_F32;
       L.y_stride = d.hidden;
     }
@@ -456,7 +530,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
       StackLinear &L = add(l, ULLM_CUDA_STACK_LINEAR_GATE_UP, 2ull * d.ffn, d.hidden, 2 * fl, d.hidden, d.tp_rank * fl, 0, false);
       L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
       L.epilogue = ULLM_CUDA_EPILOGUE_SWIGLU;  // writes silu(gate) * up: [m, ffn/tp]
-      L.in_off = act_o;
+      L.in_off = act_h1;
       L.x_dtype = ULLM_CUDA_DTYPE_F32;
       L.x_stride = d.hidden;
       L.out_off = act_gu;
@@ -469,7 +543,9 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
       L.in_off = act_gu;
       L.x_dtype = ULLM_CUDA_DTYPE_BF16;
       L.x_stride = fl;
-      L.out_off = act_h;
+      L.has_residual = true;
+      L.res_off = act_h1;
+      L.out_off = act_h2;
       L.y_dtype = ULLM_CUDA_DTYPE_F32;
       L.y_stride = d.hidden;
     }
@@ -477,7 +553,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   {
     StackLinear &L = add(0, ULLM_CUDA_STACK_LINEAR_LM_HEAD, d.vocab, d.hidden, vl, d.hidden, d.tp_rank * vl, 0, false);
     L.prologue = ULLM_CUDA_PROLOGUE_RMSNORM;
-    L.in_off = act_h_v[act_sets - 1];
+    L.in_off = act_h2_v[act_sets - 1];
     L.x_dtype = ULLM_CUDA_DTYPE_F32;
     L.x_stride = d.hidden;
     L.out_is_step_output = true;
@@ -496,7 +572,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
   if (e == cudaSuccess && S->io) e = cudaEventCreateWithFlags(&S->done, cudaEventDisableTiming);
   if (e != cudaSuccess || !S->io) {
     (void)cudaGetLastError();
-    destroy_stack(S);
+    (void)destroy_stack(S, false);
     return cuda_error(sink, e, "stack allocation");
   }
   (void)cudaMemsetAsync(S->acts->ptr, 0, aoff, q->stream);
@@ -518,6 +594,11 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     off += 256;
     std::string why;
     S->push = comm_sym_setup(cm, off, &why);  // false: stay on NCCL (same verdict on every rank)
+    // how the consumers gather: per cluster from four ranks on (every block reading every rank's slots costs
+    // tp x 64 KiB of L2 reads per block and row), per block below, unless the caller forces one way
+    S->gather_cluster = t >= 4 ? 8u : 0u;
+    if (d.flags & ULLM_CUDA_STACK_FLAG_GATHER_PER_CLUSTER) S->gather_cluster = 8u;
+    if (d.flags & ULLM_CUDA_STACK_FLAG_GATHER_PER_BLOCK) S->gather_cluster = 0u;
   }
 
   // ---- reserve the GEMM path's scratch for the largest step (it cannot grow during capture) ----
@@ -532,10 +613,10 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
         if (tokens == d.max_tokens) break;
       }
     }
-    e = gemm_reserve_scratch(ctx, need);
+    e = gemm_reserve_scratch(&q->scratch, need);
     if (e != cudaSuccess) {
       (void)cudaGetLastError();
-      destroy_stack(S);
+      (void)destroy_stack(S, false);
       return cuda_error(sink, e, "stack scratch allocation");
     }
   }
@@ -560,12 +641,19 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
       pieces.push_back({L.row_begin, L.n});
     }
     e = build_weight(S, L, pieces, scratch, codes, scratch_elems);
+    if (e == cudaSuccess && L.has_norm) {  // gamma = bf16(1 + z / 8), the same vector on every rank
+      launch_synth_weights(q->stream, d.seed, L.norm_tensor_id, 0, L.k, 1.0f, scratch);
+      gamma_kernel<<<(unsigned)((L.k + 255) / 256), 256, 0, q->stream>>>(
+          scratch, reinterpret_cast<__nv_bfloat16 *>(static_cast<uint8_t *>(S->weights->ptr) + L.norm_off), L.k);
+      e = cudaGetLastError();
+      if (e == cudaSuccess) e = cudaStreamSynchronize(q->stream);
+    }
   }
   if (scratch) (void)cudaFree(scratch);
   if (codes) (void)cudaFree(codes);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
-    destroy_stack(S);
+    (void)destroy_stack(S, false);
     return cuda_error(sink, e, "stack weight generation");
   }
   ctx->live_children++;
@@ -674,14 +762,19 @@ ullm_status_t ullm_cuda_stack_linear_info(ullm_cuda_stack_t *stack, uint32_t lay
   info->full_k = L.full_k;
   info->row_begin = L.row_begin;
   info->col_begin = L.col_begin;
-  info->last_input.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(L.in_is_step_input ? S->io : S->acts);
-  info->last_input.offset_bytes = L.in_is_step_input ? 0 : L.in_off;
+  info->last_input.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(S->acts);
+  info->last_input.offset_bytes = L.in_off;
   info->last_output.buffer = reinterpret_cast<ullm_cuda_buffer_t *>(L.out_is_step_output ? S->io : S->acts);
   info->last_output.offset_bytes = L.out_is_step_output ? S->io_out_off : L.out_off;
   info->input_dtype = L.x_dtype;
   info->output_dtype = L.y_dtype;
   info->prologue = L.prologue;
   info->epilogue = L.epilogue;
+  info->norm_weight.buffer = L.has_norm ? reinterpret_cast<ullm_cuda_buffer_t *>(S->weights) : nullptr;
+  info->norm_weight.offset_bytes = L.has_norm ? L.norm_off : 0;
+  info->norm_tensor_id = L.has_norm ? L.norm_tensor_id : 0;
+  info->last_residual.buffer = L.has_residual ? reinterpret_cast<ullm_cuda_buffer_t *>(S->acts) : nullptr;
+  info->last_residual.offset_bytes = L.has_residual ? L.res_off : 0;
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("stack linear info")
 }
@@ -709,10 +802,11 @@ ullm_status_t ullm_cuda_stack_destroy(ullm_cuda_stack_t **stack, ullm_cuda_error
   Stack *S = as_stack(*stack);
   if (S == nullptr) return write_error(sink, ULLM_STATUS_CUDA_INVALID_HANDLE, "stack handle is not live");
   registry().remove(S);
-  Context *ctx = S->ctx;
-  destroy_stack(S);
-  ctx->live_children--;
+  const bool watched = destroy_stack(S, true);
   *stack = nullptr;
+  if (!watched)
+    return write_error(sink, ULLM_STATUS_CUDA_RUNTIME_ERROR,
+                       "stack retired without proof of completion: its memory is abandoned, not freed");
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("stack destroy")
 }

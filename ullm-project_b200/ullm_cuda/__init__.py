@@ -22,7 +22,8 @@ from . import _abi as abi
 from ._abi import (EPILOGUE_NONE, EPILOGUE_SWIGLU, DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_F8E4M3FN, DTYPE_I8, DTYPE_U8, ENCODING_AQ4,  # noqa: F401
                    ENCODING_FP8_CHANNEL, ENCODING_NVFP4, KERNEL_AUTO, KERNEL_GEMM, KERNEL_MATVEC, LINEAR_DOWN,
                    LINEAR_GATE_UP, LINEAR_LM_HEAD, LINEAR_O, LINEAR_QKV, PROLOGUE_NONE, PROLOGUE_RMSNORM,
-                   PROLOGUE_SWIGLU, STACK_FLAG_KEEP_ACTIVATIONS, STACK_FLAG_NCCL_ONLY, STACK_FLAG_NO_GRAPH)
+                   PROLOGUE_SWIGLU, STACK_FLAG_GATHER_PER_BLOCK, STACK_FLAG_GATHER_PER_CLUSTER,
+                   STACK_FLAG_KEEP_ACTIVATIONS, STACK_FLAG_NCCL_ONLY, STACK_FLAG_NO_GRAPH)
 
 ERROR_CAPACITY = 512
 
@@ -169,6 +170,10 @@ class Context(_Handle):
         _call("ullm_cuda_context_probe", self._h, C.byref(r))
         return r
 
+    def set_wait_limit(self, limit_ms: int):
+        """Limit of every device-side wait of kernels launched for this context from now on."""
+        _call("ullm_cuda_context_set_wait_limit", self._h, int(limit_ms))
+
     def queue(self) -> "Queue":
         return Queue(self)
 
@@ -193,12 +198,13 @@ class Completion(_Handle):
     _destroy = "ullm_cuda_completion_destroy"
 
     def wait(self, timeout_ms: int = 60000) -> abi.CompletionResult:
-        """Consumes the handle unless the wait times out."""
+        """Consumes the handle whatever the outcome, a timeout included (the reference's rule:
+        crates/ullm-hip/src/lib.rs:404-441 drops the completion after every wait)."""
         r = abi.CompletionResult(struct_size=C.sizeof(abi.CompletionResult), abi_version=abi.ABI_VERSION)
         s, buf = _sink()
         raw = abi.load().ullm_cuda_completion_wait(self._h, min(int(timeout_ms), 0xFFFFFFFF), C.byref(r), C.byref(s))
-        if raw != abi.CUDA_TIMEOUT:
-            self._h = C.c_void_p(None)
+        self._h = C.c_void_p(None)
+        self.last_result = r
         _check(raw, s, buf)
         return r
 
@@ -289,6 +295,15 @@ class Queue(_Handle):
         Calls on one device share that array, so they must not overlap on the GPU."""
         _call("ullm_cuda_linear_enqueue_static_scratch", self._h, C.byref(desc))
 
+    def linear_enqueue_partial(self, desc: abi.LinearDesc, slots: abi.Slots):
+        """Producer half of the fused all-reduce: the fp32 results go to slot `slots.rank` as {value, tag} pairs."""
+        _call("ullm_cuda_linear_enqueue_partial", self._h, C.byref(desc), C.byref(slots))
+
+    def linear_enqueue_reduced(self, desc: abi.LinearDesc, slots: abi.Slots, reduced_out: abi.Tensor | None = None):
+        """Consumer half: the input is bf16(residual + sum of the ranks' slots); `reduced_out` receives that sum."""
+        _call("ullm_cuda_linear_enqueue_reduced", self._h, C.byref(desc), C.byref(slots),
+              reduced_out if reduced_out is not None else abi.Tensor(None, 0))
+
     def linear_submit(self, desc: abi.LinearDesc) -> Completion:
         c = Completion()
         _call("ullm_cuda_linear_submit", self._h, C.byref(desc), C.byref(c._h))
@@ -308,7 +323,8 @@ def weight_bytes(encoding: int, n: int, k: int):
 
 def linear_desc(weight: abi.Weight, m: int, x: abi.Tensor, y: abi.Tensor, *, input_dtype=DTYPE_BF16,
                 output_dtype=DTYPE_BF16, prologue=PROLOGUE_NONE, kernel=KERNEL_AUTO, rms_eps=1e-5,
-                input_row_stride=0, output_row_stride=0, epilogue=EPILOGUE_NONE) -> abi.LinearDesc:
+                input_row_stride=0, output_row_stride=0, epilogue=EPILOGUE_NONE, norm_weight: abi.Tensor | None = None,
+                residual: abi.Tensor | None = None, residual_row_stride=0) -> abi.LinearDesc:
     d = abi.LinearDesc()
     d.struct_size = C.sizeof(abi.LinearDesc)
     d.abi_version = abi.ABI_VERSION
@@ -324,7 +340,23 @@ def linear_desc(weight: abi.Weight, m: int, x: abi.Tensor, y: abi.Tensor, *, inp
     d.kernel = kernel
     d.rms_eps = rms_eps
     d.epilogue = epilogue
+    if norm_weight is not None:
+        d.norm_weight = norm_weight
+    if residual is not None:
+        d.residual = residual
+    d.residual_row_stride = residual_row_stride
     return d
+
+
+def slots_desc(slots: abi.Tensor, rank_stride_bytes: int, ranks: int, *, rank: int = 0, tag: int = 1,
+               gather: int = 0) -> abi.Slots:
+    s = abi.Slots()
+    s.struct_size = C.sizeof(abi.Slots)
+    s.abi_version = abi.ABI_VERSION
+    s.slots = slots
+    s.rank_stride_bytes = rank_stride_bytes
+    s.ranks, s.rank, s.tag, s.gather = ranks, rank, tag, gather
+    return s
 
 
 def linear_supports(desc: abi.LinearDesc) -> int:

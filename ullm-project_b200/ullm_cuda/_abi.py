@@ -28,6 +28,8 @@ KERNEL_AUTO, KERNEL_MATVEC, KERNEL_GEMM = 0, 1, 2
 STACK_FLAG_NO_GRAPH = 1
 STACK_FLAG_KEEP_ACTIVATIONS = 2
 STACK_FLAG_NCCL_ONLY = 4
+STACK_FLAG_GATHER_PER_BLOCK = 8
+STACK_FLAG_GATHER_PER_CLUSTER = 16
 LINEAR_QKV, LINEAR_O, LINEAR_GATE_UP, LINEAR_DOWN, LINEAR_LM_HEAD = 0, 1, 2, 3, 4
 COMM_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -75,7 +77,13 @@ class LinearDesc(C.Structure):
     _fields_ = [("struct_size", u32), ("abi_version", u32), ("weight", Weight), ("m", u64), ("input", Tensor),
                 ("input_row_stride", u64), ("output", Tensor), ("output_row_stride", u64), ("input_dtype", u32),
                 ("output_dtype", u32), ("prologue", u32), ("kernel", u32), ("rms_eps", C.c_float),
-                ("epilogue", u32), ("reserved", u32 * 4)]
+                ("epilogue", u32), ("norm_weight", Tensor), ("residual", Tensor), ("residual_row_stride", u64),
+                ("reserved", u32 * 4)]
+
+
+class Slots(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("slots", Tensor), ("rank_stride_bytes", u64),
+                ("ranks", u32), ("rank", u32), ("tag", u32), ("gather", u32), ("reserved", u32 * 4)]
 
 
 class StackDesc(C.Structure):
@@ -89,13 +97,14 @@ class StackLinearInfo(C.Structure):
     _fields_ = [("struct_size", u32), ("abi_version", u32), ("weight", Weight), ("tensor_id", u64), ("full_n", u64),
                 ("full_k", u64), ("row_begin", u64), ("col_begin", u64), ("last_input", Tensor),
                 ("last_output", Tensor), ("input_dtype", u32), ("output_dtype", u32), ("prologue", u32),
-                ("epilogue", u32), ("reserved", u32 * 4)]
+                ("epilogue", u32), ("norm_weight", Tensor), ("last_residual", Tensor), ("norm_tensor_id", u64),
+                ("reserved", u32 * 4)]
 
 
 # sizes pinned in the header's static_asserts
 EXPECTED_SIZES = {
     ErrorSink: 48, VersionInfo: 32, BackendProbeResult: 64, ContextProbeResult: 32, Tensor: 16, Weight: 56,
-    CompletionResult: 56, LinearDesc: 160, StackDesc: 88, StackLinearInfo: 168,
+    CompletionResult: 56, LinearDesc: 200, StackDesc: 88, StackLinearInfo: 208, Slots: 64,
 }
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -112,6 +121,7 @@ SIGNATURES = {
     "ullm_cuda_context_probe": [vp, P(ContextProbeResult), SINK],
     "ullm_cuda_context_create": [u32, P(vp), SINK],
     "ullm_cuda_context_destroy": [P(vp), SINK],
+    "ullm_cuda_context_set_wait_limit": [vp, u32, SINK],
     "ullm_cuda_queue_create": [vp, P(vp), SINK],
     "ullm_cuda_queue_destroy": [P(vp), SINK],
     "ullm_cuda_buffer_alloc": [vp, u64, P(vp), SINK],
@@ -139,6 +149,8 @@ SIGNATURES = {
     "ullm_cuda_linear_enqueue": [vp, P(LinearDesc), SINK],
     "ullm_cuda_linear_submit": [vp, P(LinearDesc), P(vp), SINK],
     "ullm_cuda_linear_enqueue_static_scratch": [vp, P(LinearDesc), SINK],
+    "ullm_cuda_linear_enqueue_partial": [vp, P(LinearDesc), P(Slots), SINK],
+    "ullm_cuda_linear_enqueue_reduced": [vp, P(LinearDesc), P(Slots), Tensor, SINK],
     "ullm_cuda_comm_unique_id": [P(C.c_uint8), SINK],
     "ullm_cuda_comm_create": [vp, P(C.c_uint8), u32, u32, P(vp), SINK],
     "ullm_cuda_comm_all_reduce": [vp, vp, Tensor, u64, u32, SINK],
