@@ -20,6 +20,16 @@ def check(y, ref, what=""):
     return st
 
 
+def check_norm(y, ref, what=""):
+    """For outputs behind an RMSNorm: the device normalises in fp32, the oracle in fp64, so a handful of normalised
+    activations round to the neighbouring bf16 value and move an output that sits on a rounding boundary by one
+    more ulp.  Mean error and NaN classes as everywhere; a few element-wise outliers are allowed."""
+    st = o.error_stats(y, ref)
+    assert st["nan"] == 0 and st["inf"] == 0 and st["mean_abs"] <= 1e-3 and st["max_rel_floored"] <= 2e-2 and \
+        st["outliers"] <= max(2, st["n"] // 2000), (what, st)
+    return st
+
+
 # boundary sets: N over tile/warp-group edges, K over piece/iteration edges, every M the matvec serves
 CASES = [(1, 1, 128), (1, 3, 256), (2, 17, 384), (3, 255, 1024), (4, 256, 1152), (5, 257, 2048),
          (7, 73, 4096), (8, 37, 3584), (1, 4096, 4096), (8, 1024, 4096), (1, 613, 14336), (3, 64, 14336)]
@@ -213,10 +223,10 @@ def test_rmsnorm_weight_and_residual(gpu, encoding, m, kernel):
         y, _ = run_linear(ctx, q, dw, x, x_dtype=U.DTYPE_F32, y_dtype=ydt, prologue=U.PROLOGUE_RMSNORM, kernel=kernel,
                           gamma=gamma, residual=res)
         ref = oracle_linear(x, wdq, U.PROLOGUE_RMSNORM, x_is_f32=True, out=out, gamma=gamma, residual=res)
-        check(y, ref, (encoding, m, kernel, out))
+        check_norm(y, ref, (encoding, m, kernel, out))
     # the weight vector alone, and the residual alone (in place: the residual aliases the output)
     y, _ = run_linear(ctx, q, dw, x, x_dtype=U.DTYPE_F32, prologue=U.PROLOGUE_RMSNORM, kernel=kernel, gamma=gamma)
-    check(y, oracle_linear(x, wdq, U.PROLOGUE_RMSNORM, x_is_f32=True, gamma=gamma), "gamma only")
+    check_norm(y, oracle_linear(x, wdq, U.PROLOGUE_RMSNORM, x_is_f32=True, gamma=gamma), "gamma only")
     xb = o.bf16_round(x)
     ybuf, xbuf = ctx.alloc(m * n * 4), ctx.alloc(m * k * 2)
     q.upload(ybuf.at(0), res)

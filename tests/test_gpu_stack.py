@@ -138,8 +138,11 @@ def test_one_full_width_layer_spot_check(gpu):
             rows = np.concatenate([cols, n // 2 + cols]) if pair else cols  # gate rows, then the matching up rows
             wr = np.stack([o.synth_weights(SEED, info.tensor_id, 1, k, row0=int(r))[0] for r in rows])
             v, s = oracle_quantize(wr, encoding)
+            gamma = o.bf16_bits_to_f32(q.download(info.norm_weight, (k,), np.uint16)) if info.norm_weight.buffer else None
+            resid = q.download(info.last_residual, (2, n), np.float32)[:, cols] if info.last_residual.buffer else None
             ref = oracle_linear(xin, oracle_dequantize(v, s, encoding), info.prologue, x_is_f32=in_dt == np.float32,
-                                out="f32" if out_dt == np.float32 else "bf16", epilogue=info.epilogue)
+                                out="f32" if out_dt == np.float32 else "bf16", epilogue=info.epilogue, gamma=gamma,
+                                residual=resid)
             stt = o.error_stats(yout[:, cols], ref)
             assert stt["pass"], (encoding, which, stt)
         st.close()
