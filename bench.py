@@ -451,13 +451,80 @@ def run_single_matvec(U, args):
     ctx.close()
 
 
+def run_single_gather(U, args):
+    """The consumer half of the fused all-reduce alone, on one GPU: the slots of `--ranks` ranks are filled once
+    (values and tags in place), then a QKV-shaped linear (N = --n, K = --k, RMSNorm with weight, residual) gathers
+    them `--steps` times per graph replay over enough weight copies to exceed 2x L2.  Shows what the gather costs
+    on top of the plain matvec of the same shape (no NVLink and no skew between ranks in this figure)."""
+    ctx = U.Context(0)
+    q = ctx.queue()
+    enc_id = U.ENCODING_AQ4 if args.enc == "aq4" else U.ENCODING_FP8_CHANNEL
+    n, k, m, ranks = args.n, args.k, args.batch, args.ranks
+    vb, sb = U.weight_bytes(enc_id, n, k)
+    copies = max(2, int(2 * 130e6 // (vb + sb)) + 1)
+    src = ctx.alloc(n * k * 4)
+    q.synth_weights(SEED, 4242, 0, n * k, 0.02, src.at(0))
+    stride = m * k * 8
+    slots = ctx.alloc(ranks * stride)
+    pairs = np.zeros((ranks, m * k, 2), np.uint32)
+    pairs[:, :, 0] = (np.random.default_rng(SEED).standard_normal((ranks, m * k)).astype(np.float32) / np.float32(ranks)).view(np.uint32)
+    pairs[:, :, 1] = 9
+    q.upload(slots.at(0), pairs)
+    resid, gam = ctx.alloc(m * k * 4), ctx.alloc(k * 2)
+    q.synth_weights(SEED, 4250, 0, m * k, 1.0, resid.at(0))
+    q.fill(gam.at(0), 0x3F, k * 2)  # bf16 0x3F3F = 0.746
+    xdummy, yb = ctx.alloc(m * k * 4), ctx.alloc(m * n * 2)
+    bufs, descs = [], []
+    for _ in range(copies):
+        v, sc = ctx.alloc(vb), ctx.alloc(sb)
+        wd = U.weight_desc(enc_id, n, k, v.at(0), sc.at(0))
+        q.quantize(src.at(0), wd)
+        bufs += [v, sc]
+        descs.append(U.linear_desc(wd, m, xdummy.at(0), yb.at(0), input_dtype=U.DTYPE_F32, prologue=U.PROLOGUE_RMSNORM,
+                                   norm_weight=gam.at(0), residual=resid.at(0)))
+    sl = U.slots_desc(slots.at(0), stride, ranks, tag=9, gather=1 if args.gather == "cluster" else 0)
+    q.linear_enqueue_reduced(descs[0], sl)
+    assert q.synchronize().device_flags == 0
+    q.capture_begin()
+    for d in descs:
+        q.linear_enqueue_reduced(d, sl)
+    g = q.capture_end()
+    for _ in range(3):
+        g.launch(q)
+    q.synchronize()
+    a = q.signal()
+    for _ in range(max(args.steps, 1)):
+        g.launch(q)
+    b = q.signal()
+    b.query(600000)
+    us = b.elapsed_ms_since(a) * 1e3 / (max(args.steps, 1) * copies)
+    a.close()
+    b.close()
+    g.close()
+    algo = vb + sb + ranks * m * k * 8 + m * k * 4 + m * n * 2
+    peak, peak_src = peaks()
+    print(json.dumps({
+        "metric": "gathering matvec HBM GB/s", "value": algo / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": 3, "ms_per_step": us * copies / 1e3, "higher_is_better": True,
+        "config": {"workload": f"{args.enc} matvec M={m} N={n} K={k} gathering {ranks} ranks' slots per {args.gather}",
+                   "weight_copies": copies},
+        "roofline": {"bound": "hbm", "achieved": algo / us / 1e3, "peak": peak, "unit": "GB/s", "frac": algo / us / 1e3 / peak,
+                     "traffic": None, "peak_source": peak_src, "us_per_launch": us, "algorithmic_bytes": algo},
+        "gpu_launches": copies * (max(args.steps, 1) + 4)}), flush=True)
+    for buf in bufs + [src, slots, resid, gam, xdummy, yb]:
+        buf.close()
+    q.close()
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS) + ["matvec", "gemm"])
+    ap.add_argument("--workload", default="stack70b-fp8", choices=sorted(WORKLOADS) + ["matvec", "gemm", "gather"])
+    ap.add_argument("--ranks", type=int, default=8, help="gather workload: ranks whose slots are summed")
     ap.add_argument("--enc", default="fp8", choices=["fp8", "aq4"], help="matvec workload: weight encoding")
     ap.add_argument("--kernel", default="auto", choices=["auto", "matvec", "gemm"],
                     help="matvec workload: kernel behind the linear op (auto: by token count)")
@@ -480,6 +547,9 @@ def main():
         return
     if args.workload == "gemm":
         run_single_gemm(U, args)
+        return
+    if args.workload == "gather":
+        run_single_gather(U, args)
         return
     shape_name, enc, descr = WORKLOADS[args.workload]
     shape = getattr(U, shape_name)
