@@ -189,6 +189,43 @@ class CpuStack:
         return time.perf_counter() - t0
 
 
+def cpu_single_ops(threads_all):
+    """The plain-C port on the single-op benchmark configurations (1: AQ4 matvec 4096x4096; 2: FP8 matvec
+    14336x4096, M = 1/4/8; 3: AQ4 GEMM 14336x4096 and 4096x14336 on a 64-token sample of the 2048 tokens, scaled
+    linearly in M), once with every host core and once on a single thread.  Seconds per call."""
+    import oracle_c as oc
+    rng = np.random.default_rng(SEED + 1)
+    out = {}
+
+    def weight(enc, n, k):
+        if enc == "aq4":
+            return np.frombuffer(rng.bytes(n * (k // 2)), np.uint8).reshape(n, k // 2), np.full((n, k // 128), 0.003, np.float16)
+        return np.frombuffer(rng.bytes(n * k), np.uint8).reshape(n, k) & np.uint8(0xF7), np.full(n, 1e-4, np.float32)
+
+    cases = [("config1_aq4_m1_k4096_n4096", "aq4", 1, 4096, 4096, 1.0), ("config2_fp8_m1_k4096_n14336", "fp8", 1, 14336, 4096, 1.0),
+             ("config2_fp8_m4_k4096_n14336", "fp8", 4, 14336, 4096, 1.0), ("config2_fp8_m8_k4096_n14336", "fp8", 8, 14336, 4096, 1.0),
+             ("config3_aq4_m2048_k4096_n14336", "aq4", 64, 14336, 4096, 32.0), ("config3_aq4_m2048_k14336_n4096", "aq4", 64, 4096, 14336, 32.0)]
+    for name, enc, m, n, k, scale in cases:
+        w = weight(enc, n, k)
+        x = oc.synth_activations_bits(SEED, 6000 + m, m, k)
+        fn = oc.linear_aq4 if enc == "aq4" else oc.linear_fp8
+        rec = {}
+        for label, threads in (("all_cores", threads_all), ("single_thread", 1)):
+            oc.set_num_threads(threads)
+            fn(x, w[0], w[1])
+            reps = 3 if label == "all_cores" else 1
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn(x, w[0], w[1])
+            rec[label + "_ms"] = (time.perf_counter() - t0) / reps * 1e3 * scale
+        rec["cores"] = threads_all
+        if scale != 1.0:
+            rec["sample"] = f"{m} of the tokens, scaled x{scale:.0f}"
+        out[name] = rec
+    oc.set_num_threads(threads_all)
+    return out
+
+
 def reference_config(args, shape, enc, descr, world):
     """The `config` object both arms print (the driver compares them key by key)."""
     return {"workload": f"{descr}, batch {args.batch}, tensor-parallel over {world} GPU(s)", "batch": args.batch,
@@ -740,6 +777,7 @@ def main():
         t0 = time.perf_counter()
         cpu.layer_pass(h)
         t1 = time.perf_counter() - t0
+        line["cpu_single_ops"] = cpu_single_ops(cpu.threads)
         line["cpu_baseline"] = {
             "value": B / (t * scale), "unit": "tokens/s", "cores": cpu.threads, "kind": "port",
             "single_thread_value": B / (t1 * scale),

@@ -94,6 +94,8 @@ typedef struct ullm_cuda_completion_t ullm_cuda_completion_t;
 typedef struct ullm_cuda_graph_t ullm_cuda_graph_t;
 typedef struct ullm_cuda_comm_t ullm_cuda_comm_t;
 typedef struct ullm_cuda_stack_t ullm_cuda_stack_t;
+typedef struct ullm_cuda_prepared_t ullm_cuda_prepared_t;
+typedef struct ullm_cuda_event_t ullm_cuda_event_t;
 
 /* identical layout to ullm_error_sink_t (hip.h:48-55): 48 bytes, align 8 */
 typedef struct ullm_cuda_error_sink_t {
@@ -272,6 +274,35 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_dequantize(ullm_cuda_queue_t *queue, const
                                    ullm_cuda_tensor_t out, uint32_t out_dtype,
                                    ullm_cuda_error_sink_t *error_sink);
 
+/* ---- weights from a safetensors file, quantised on the device while they load -------------------
+ * No counterpart in the reference yet; its plan names safetensors as the weight source and on-load conversion as
+ * the place where quantised encodings are produced (docs/plans/main-plan.md:26, :76, :112).
+ * The file is read by the library during the call (header: 8-byte little-endian length + JSON; tensor data
+ * follows); nothing of it is kept afterwards.  Source dtypes F32, F16 and BF16 are accepted.  F8_E4M3 / F8_E5M2
+ * payloads and the "fnuz" flavours are rejected by name (ULLM_STATUS_UNSUPPORTED): an e4m3fn code must never be
+ * read as e4m3fnuz or the other way round (docs/compatibility/amd-gpu.md:88-89). */
+typedef struct ullm_cuda_safetensors_info_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t dtype;       /* ULLM_CUDA_DTYPE_* of the stored tensor */
+  uint32_t rank;        /* 1 or 2 (a rank-1 tensor is reported as [1, cols]) */
+  uint64_t rows;
+  uint64_t cols;
+  uint64_t data_offset; /* of the tensor's first byte, from the start of the file */
+  uint64_t data_bytes;
+  uint32_t reserved[4];
+} ullm_cuda_safetensors_info_t;
+/* Header only: no device is touched.  ULLM_STATUS_INVALID_ARGUMENT for a file that is not safetensors or a name it
+ * does not hold (the sink names what was wrong). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_safetensors_find(const char *path, const char *tensor_name,
+                                         ullm_cuda_safetensors_info_t *info, ullm_cuda_error_sink_t *error_sink);
+/* Reads tensor [N, K] in row chunks through the queue's pinned staging memory, converts to fp32 on the device and
+ * quantises each chunk straight into weight.values / weight.scales (the same quantiser as ullm_cuda_quantize, so
+ * the bytes equal quantising the fp32 tensor in one piece).  weight.n / weight.k must equal the stored shape.
+ * Synchronous with respect to the caller like ullm_cuda_buffer_upload. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_quantize_safetensors(ullm_cuda_queue_t *queue, const char *path, const char *tensor_name,
+                                             const ullm_cuda_weight_t *weight, ullm_cuda_error_sink_t *error_sink);
+
 /* ---- the linear op: y[M,N] = prologue(x)[M,K] . W'[N,K]^T, fp32 accumulate ------ */
 #define ULLM_CUDA_PROLOGUE_NONE UINT32_C(0)
 #define ULLM_CUDA_PROLOGUE_RMSNORM UINT32_C(1) /* x <- bf16(x * rsqrt(mean(x^2) + eps) * gamma); gamma = 1 without norm_weight */
@@ -344,6 +375,93 @@ ULLM_CUDA_API ullm_status_t ullm_cuda_linear_submit(ullm_cuda_queue_t *queue, co
 ULLM_CUDA_API ullm_status_t ullm_cuda_linear_enqueue_static_scratch(ullm_cuda_queue_t *queue,
                                                                     const ullm_cuda_linear_desc_t *desc,
                                                                     ullm_cuda_error_sink_t *error_sink);
+
+/* ---- coarse command lists: prepare once, submit many times ---------------------------------------
+ * The call unit the reference's runtime design fixes for its C ABI (docs/architecture/runtime.md:77-79): not one
+ * call per kernel but a prepared plan of several ops.  PREPARE copies the reusable metadata (op kinds, shapes,
+ * dtypes, encodings, prologues / epilogues) into storage the library owns and chooses every kernel, so that a
+ * missing capability shows before anything runs; it keeps no pointer into the caller's arrays.  SUBMIT copies,
+ * during the call, the resource bindings with the access mode each declares (AccessMode,
+ * crates/ullm-core/src/handles.rs:12-16) and the dependency events, checks them against what each op needs, makes
+ * the queue wait for the dependencies, enqueues all ops in order and returns a completion EVENT.  A synchronous
+ * validation / enqueue failure is the status of submit itself; a failure after enqueue (a device-side wait that
+ * gave up) is stored in the event, which owns its diagnostic (runtime.md:79), and read with event_query /
+ * event_wait.  The context's executor owns every in-flight submission: destroying the event does not stop it from
+ * being watched, and ullm_cuda_context_shutdown refuses new prepares / submits, drains what is in flight, and
+ * collects the terminal statuses (runtime.md:63). */
+#define ULLM_CUDA_ACCESS_READ UINT32_C(1) /* the values of ULLM_ACCESS_* (crates/ullm-hip-sys/src/bindings.rs:27-29) */
+#define ULLM_CUDA_ACCESS_WRITE UINT32_C(2)
+#define ULLM_CUDA_ACCESS_READ_WRITE UINT32_C(3)
+
+#define ULLM_CUDA_PLAN_OP_HAS_NORM_WEIGHT UINT32_C(1) /* the RMSNorm prologue takes a weight vector */
+#define ULLM_CUDA_PLAN_OP_HAS_RESIDUAL UINT32_C(2)    /* a residual is added to the result */
+
+typedef struct ullm_cuda_plan_op_t { /* one quantised linear of a plan: metadata only, no buffers */
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t encoding;
+  uint32_t group_size;
+  uint64_t n;
+  uint64_t k;
+  uint64_t m;
+  uint32_t input_dtype;
+  uint32_t output_dtype;
+  uint32_t prologue;
+  uint32_t epilogue;
+  uint32_t kernel; /* ULLM_CUDA_KERNEL_AUTO or a forced kernel */
+  uint32_t flags;  /* ULLM_CUDA_PLAN_OP_* */
+  float rms_eps;
+  uint32_t reserved[5];
+} ullm_cuda_plan_op_t;
+
+/* what a binding feeds */
+#define ULLM_CUDA_SLOT_WEIGHT_VALUES UINT32_C(0)
+#define ULLM_CUDA_SLOT_WEIGHT_SCALES UINT32_C(1)
+#define ULLM_CUDA_SLOT_INPUT UINT32_C(2)
+#define ULLM_CUDA_SLOT_OUTPUT UINT32_C(3)
+#define ULLM_CUDA_SLOT_NORM_WEIGHT UINT32_C(4)
+#define ULLM_CUDA_SLOT_RESIDUAL UINT32_C(5)
+
+typedef struct ullm_cuda_binding_t {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  uint32_t op_index; /* which op of the plan */
+  uint32_t slot;     /* ULLM_CUDA_SLOT_* */
+  uint32_t access;   /* ULLM_CUDA_ACCESS_*: inputs must permit reading, the output writing; an output that
+                        is also the op's residual must be READ_WRITE */
+  uint32_t reserved0;
+  ullm_cuda_tensor_t tensor;
+  uint32_t reserved[4];
+} ullm_cuda_binding_t;
+
+/* Copies `count` op descriptions (1 .. 4096) and selects their kernels.  ULLM_STATUS_UNSUPPORTED names the first op
+ * no kernel serves. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_prepare(ullm_cuda_context_t *context, const ullm_cuda_plan_op_t *ops, uint32_t count,
+                                ullm_cuda_prepared_t **prepared, ullm_cuda_error_sink_t *error_sink);
+ULLM_CUDA_API ullm_status_t ullm_cuda_prepared_destroy(ullm_cuda_prepared_t **prepared, ullm_cuda_error_sink_t *error_sink);
+/* One submission of the whole plan on `queue`, after the `wait_count` events given (which may belong to other
+ * queues of the context).  Every slot an op needs must be bound exactly once, with an access mode that permits
+ * what the op does with it; an op must not write a span another binding of the same op reads, unless that is the
+ * declared READ_WRITE output / residual pair.  `event` may be NULL when the caller will not observe completion. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_submit(ullm_cuda_queue_t *queue, ullm_cuda_prepared_t *prepared,
+                               const ullm_cuda_binding_t *bindings, uint32_t binding_count,
+                               ullm_cuda_event_t *const *wait_events, uint32_t wait_count, ullm_cuda_event_t **event,
+                               ullm_cuda_error_sink_t *error_sink);
+#define ULLM_CUDA_EVENT_PENDING UINT32_C(0)
+#define ULLM_CUDA_EVENT_SUCCESS UINT32_C(1)
+#define ULLM_CUDA_EVENT_FAILURE UINT32_C(2)
+/* Never consumes the event.  state: pending, success, or failure (then the sink receives the stored diagnostic
+ * and the return value is the stored status, e.g. ULLM_STATUS_CUDA_DEVICE_FLAGGED). */
+ULLM_CUDA_API ullm_status_t ullm_cuda_event_query(ullm_cuda_event_t *event, uint32_t *state, ullm_cuda_error_sink_t *error_sink);
+/* Polls up to timeout_ms (0 = one poll): OK on success, ULLM_STATUS_CUDA_TIMEOUT while pending, the stored status on failure. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_event_wait(ullm_cuda_event_t *event, uint32_t timeout_ms, ullm_cuda_error_sink_t *error_sink);
+/* Drops the caller's reference; the executor keeps watching the submission until it completes or the context shuts down. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_event_destroy(ullm_cuda_event_t **event, ullm_cuda_error_sink_t *error_sink);
+/* Closing state: new prepares and submits of this context are refused from now on; waits up to timeout_ms for every
+ * in-flight submission (ULLM_STATUS_CUDA_TIMEOUT if some are still pending: call again); reports how many completed
+ * with a failure.  The context can be destroyed afterwards like any other. */
+ULLM_CUDA_API ullm_status_t ullm_cuda_context_shutdown(ullm_cuda_context_t *context, uint32_t timeout_ms, uint32_t *failed_submissions,
+                                         ullm_cuda_error_sink_t *error_sink);
 
 /* ---- the two halves of the fused all-reduce, as single ops --------------------------------------
  * No counterpart in the reference (it has no multi-GPU code).  The tensor-parallel stack below sums the partial
@@ -504,6 +622,9 @@ static_assert(offsetof(ullm_cuda_linear_desc_t, input) == 72U, "linear input off
 static_assert(offsetof(ullm_cuda_linear_desc_t, output) == 96U, "linear output offset changed");
 static_assert(offsetof(ullm_cuda_linear_desc_t, input_dtype) == 120U, "linear input_dtype offset changed");
 static_assert(sizeof(ullm_cuda_slots_t) == 64U, "slots descriptor ABI layout changed");
+static_assert(sizeof(ullm_cuda_plan_op_t) == 88U, "plan op ABI layout changed");
+static_assert(sizeof(ullm_cuda_safetensors_info_t) == 64U, "safetensors info ABI layout changed");
+static_assert(sizeof(ullm_cuda_binding_t) == 56U, "binding ABI layout changed");
 static_assert(sizeof(ullm_cuda_stack_desc_t) == 88U, "stack descriptor ABI layout changed");
 static_assert(sizeof(ullm_cuda_stack_linear_info_t) == 208U, "stack linear info ABI layout changed");
 #endif

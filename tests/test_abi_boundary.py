@@ -38,7 +38,9 @@ def test_struct_layouts_match_the_header_pins():
                "ullm_cuda_context_probe_result_t": abi.ContextProbeResult, "ullm_cuda_tensor_t": abi.Tensor,
                "ullm_cuda_weight_t": abi.Weight, "ullm_cuda_completion_result_t": abi.CompletionResult,
                "ullm_cuda_linear_desc_t": abi.LinearDesc, "ullm_cuda_stack_desc_t": abi.StackDesc,
-               "ullm_cuda_stack_linear_info_t": abi.StackLinearInfo, "ullm_cuda_slots_t": abi.Slots}
+               "ullm_cuda_stack_linear_info_t": abi.StackLinearInfo, "ullm_cuda_slots_t": abi.Slots,
+               "ullm_cuda_plan_op_t": abi.PlanOp, "ullm_cuda_binding_t": abi.Binding,
+               "ullm_cuda_safetensors_info_t": abi.SafetensorsInfo}
     assert set(pins) == set(by_name)
     for name, cls in by_name.items():
         assert C.sizeof(cls) == int(pins[name]) == abi.EXPECTED_SIZES[cls], name

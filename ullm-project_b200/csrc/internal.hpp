@@ -88,6 +88,7 @@ constexpr int kMaxDevices = 64;
 constexpr uint32_t kDefaultWaitLimitMs = 20000;
 
 struct Queue;
+struct Submission;
 
 struct Context {
   uint32_t magic = kMagicContext;
@@ -106,6 +107,9 @@ struct Context {
   std::vector<cudaEvent_t> event_pool;
   std::vector<Queue *> queues;  // live queues (guarded by mutex): buffer_free checks that they are idle
   std::atomic<uint64_t> live_children{0};
+  // the executor of the command-list path: every submission in flight, watched until it completes
+  std::atomic<bool> closing{false};
+  std::vector<Submission *> in_flight;  // guarded by mutex
 };
 
 // Device scratch of the GEMM path (activation planes, token scales, gate|up pairs, split-K partials and the
@@ -337,6 +341,13 @@ void launch_aq4_unpack(cudaStream_t s, const uint8_t *values, uint64_t bytes, in
 void launch_aq4_pack(cudaStream_t s, const int8_t *src, uint64_t bytes, uint8_t *values);
 void launch_dequantize(cudaStream_t s, uint32_t encoding, const uint8_t *values, const void *scales, uint64_t n,
                        uint64_t k, void *out, uint32_t out_dtype);
+
+// ---- the linear op's shared entry points (linear.cu), used by the command-list path (plan.cu)
+ullm_status_t enqueue_linear_desc(Queue *q, const ullm_cuda_linear_desc_t *desc, sink_t *sink);
+ullm_status_t linear_shape_check(const ullm_cuda_linear_desc_t *desc, uint32_t *kernel, sink_t *sink);
+// Reads and clears the context's device-side failure words; non-zero = some kernel gave up a bounded wait.
+// Re-arms the device-resident abort word behind `stream` (or at once when it is null).
+uint32_t take_device_flags(Context *ctx, cudaStream_t stream, uint32_t (&words)[4]);
 
 // comm internals used by the stack
 struct Comm;

@@ -136,6 +136,12 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   return ULLM_STATUS_OK;
 }
 
+// Validates a descriptor against the queue's context and enqueues it (the body of ullm_cuda_linear_enqueue; the
+// command-list path submits every op of a plan through it).
+ullm_status_t enqueue_linear_desc(Queue *q, const ullm_cuda_linear_desc_t *desc, sink_t *sink);
+// Shape-only validation and kernel choice (the body of ullm_cuda_linear_supports; prepare uses it).
+ullm_status_t linear_shape_check(const ullm_cuda_linear_desc_t *desc, uint32_t *kernel, sink_t *sink);
+
 static ullm_status_t enqueue_resolved(Queue *q, const Resolved &r, sink_t *sink) {
   ullm_status_t refused = ULLM_STATUS_OK;
   if (!submissions_open(sink, &refused)) return refused;
@@ -146,6 +152,21 @@ static ullm_status_t enqueue_resolved(Queue *q, const Resolved &r, sink_t *sink)
   if (launched == 0)
     return write_error(sink, ULLM_STATUS_CUDA_ZERO_DISPATCH, "linear op launched no kernel");
   return end_launch(q, sink, "linear kernel launch", static_cast<uint64_t>(launched));
+}
+
+ullm_status_t enqueue_linear_desc(Queue *q, const ullm_cuda_linear_desc_t *desc, sink_t *sink) {
+  Resolved r;
+  ullm_status_t st = resolve_linear(desc, q->ctx, true, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  return enqueue_resolved(q, r, sink);
+}
+
+ullm_status_t linear_shape_check(const ullm_cuda_linear_desc_t *desc, uint32_t *kernel, sink_t *sink) {
+  Resolved r;
+  ullm_status_t st = resolve_linear(desc, nullptr, false, sink, &r);
+  if (st != ULLM_STATUS_OK) return st;
+  if (kernel != nullptr) *kernel = r.kernel;
+  return ULLM_STATUS_OK;
 }
 
 }  // namespace ullm

@@ -230,6 +230,24 @@ Reaper &reaper() {
 
 }  // namespace
 
+uint32_t take_device_flags(Context *ctx, cudaStream_t stream, uint32_t (&words)[4]) {
+  uint32_t any = 0;
+  std::lock_guard<std::mutex> g(ctx->mutex);
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t w = const_cast<volatile uint32_t *>(ctx->host_flags)[i];
+    if (i < 4) words[i] = w;
+    any |= w;
+  }
+  if (any != 0U) {
+    for (int i = 0; i < 16; ++i) const_cast<volatile uint32_t *>(ctx->host_flags)[i] = 0U;
+    if (stream != nullptr)
+      (void)cudaMemsetAsync(ctx->abort_word, 0, sizeof(uint32_t), stream);
+    else
+      (void)cudaMemset(ctx->abort_word, 0, sizeof(uint32_t));
+  }
+  return any;
+}
+
 bool submissions_open(sink_t *sink, ullm_status_t *status) noexcept {
   if (reaper().accepting()) return true;
   *status = write_error(sink, ULLM_STATUS_CUDA_RUNTIME_ERROR,
@@ -833,12 +851,9 @@ ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint
     retire_completion(c, false);
     return write_error(sink, ULLM_STATUS_CUDA_TIMEOUT, "completion not reached before the deadline; the handle is consumed");
   }
-  uint32_t flags[16];
-  uint32_t any = 0;
-  for (int i = 0; i < 16; ++i) {
-    flags[i] = const_cast<volatile uint32_t *>(ctx->host_flags)[i];
-    any |= flags[i];
-  }
+  cudaStream_t stream = as_queue(reinterpret_cast<const ullm_cuda_queue_t *>(c_queue)) != nullptr ? c->stream : nullptr;
+  uint32_t flags[4] = {0, 0, 0, 0};
+  const uint32_t any = take_device_flags(ctx, stream, flags);
   if (result != nullptr) {
     result->dispatch_count = c->dispatch_count;
     result->copy_count = c->copy_count;
@@ -847,19 +862,11 @@ ullm_status_t ullm_cuda_completion_wait(ullm_cuda_completion_t *completion, uint
     result->terminal = 1U;
     result->device_flags = any;
   }
-  cudaStream_t stream = c->stream;
   retire_completion(c, true);
-  if (any != 0U) {
-    for (int i = 0; i < 16; ++i) const_cast<volatile uint32_t *>(ctx->host_flags)[i] = 0U;
-    // re-arm the device-side abort word behind the work that tripped it (the queue may be gone by now)
-    if (as_queue(reinterpret_cast<const ullm_cuda_queue_t *>(c_queue)) != nullptr)
-      (void)cudaMemsetAsync(ctx->abort_word, 0, sizeof(uint32_t), stream);
-    else
-      (void)cudaMemset(ctx->abort_word, 0, sizeof(uint32_t));
+  if (any != 0U)
     return errorf(sink, ULLM_STATUS_CUDA_DEVICE_FLAGGED,
                   "a kernel gave up a bounded wait (flags %08x %08x %08x %08x); results are not valid", flags[0],
                   flags[1], flags[2], flags[3]);
-  }
   return ULLM_STATUS_OK;
   ULLM_ENTRY_END("completion wait")
 }

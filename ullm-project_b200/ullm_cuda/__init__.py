@@ -170,6 +170,12 @@ class Context(_Handle):
         _call("ullm_cuda_context_probe", self._h, C.byref(r))
         return r
 
+    def shutdown(self, timeout_ms: int = 60000) -> int:
+        """Refuses new prepares / submits, drains what is in flight; returns how many submissions failed."""
+        failed = C.c_uint32(0)
+        _call("ullm_cuda_context_shutdown", self._h, int(timeout_ms), C.byref(failed))
+        return failed.value
+
     def set_wait_limit(self, limit_ms: int):
         """Limit of every device-side wait of kernels launched for this context from now on."""
         _call("ullm_cuda_context_set_wait_limit", self._h, int(limit_ms))
@@ -277,6 +283,10 @@ class Queue(_Handle):
     def quantize(self, src_f32: abi.Tensor, weight: abi.Weight):
         _call("ullm_cuda_quantize", self._h, src_f32, C.byref(weight))
 
+    def quantize_safetensors(self, path: str, name: str, weight: abi.Weight):
+        """Loads tensor `name` [N, K] of a safetensors file and quantises it on the device into `weight`."""
+        _call("ullm_cuda_quantize_safetensors", self._h, path.encode(), name.encode(), C.byref(weight))
+
     def aq4_unpack(self, weight: abi.Weight, out_i8: abi.Tensor):
         _call("ullm_cuda_aq4_unpack", self._h, C.byref(weight), out_i8)
 
@@ -364,6 +374,67 @@ def linear_supports(desc: abi.LinearDesc) -> int:
     k = C.c_uint32(0)
     _call("ullm_cuda_linear_supports", C.byref(desc), C.byref(k))
     return k.value
+
+
+def safetensors_find(path: str, name: str) -> abi.SafetensorsInfo:
+    """Dtype, shape and position of one tensor of a safetensors file (header only; no device)."""
+    info = abi.SafetensorsInfo(struct_size=C.sizeof(abi.SafetensorsInfo), abi_version=abi.ABI_VERSION)
+    _call("ullm_cuda_safetensors_find", path.encode(), name.encode(), C.byref(info))
+    return info
+
+
+def plan_op(encoding: int, m: int, n: int, k: int, *, input_dtype=DTYPE_BF16, output_dtype=DTYPE_BF16, prologue=PROLOGUE_NONE,
+            epilogue=EPILOGUE_NONE, kernel=KERNEL_AUTO, rms_eps=1e-5, norm_weight=False, residual=False) -> abi.PlanOp:
+    """One quantised linear of a plan: metadata only (the buffers arrive with each submission)."""
+    o = abi.PlanOp()
+    o.struct_size = C.sizeof(abi.PlanOp)
+    o.abi_version = abi.ABI_VERSION
+    o.encoding, o.group_size = encoding, 128 if encoding == ENCODING_AQ4 else 0
+    o.n, o.k, o.m = n, k, m
+    o.input_dtype, o.output_dtype, o.prologue, o.epilogue, o.kernel, o.rms_eps = input_dtype, output_dtype, prologue, epilogue, kernel, rms_eps
+    o.flags = (abi.PLAN_OP_HAS_NORM_WEIGHT if norm_weight else 0) | (abi.PLAN_OP_HAS_RESIDUAL if residual else 0)
+    return o
+
+
+def binding(op_index: int, slot: int, access: int, tensor: abi.Tensor) -> abi.Binding:
+    b = abi.Binding()
+    b.struct_size = C.sizeof(abi.Binding)
+    b.abi_version = abi.ABI_VERSION
+    b.op_index, b.slot, b.access, b.tensor = op_index, slot, access, tensor
+    return b
+
+
+class Event(_Handle):
+    """Completion of one submission.  Never consumed by query or wait; dropping it does not stop the context's
+    executor from watching the submission."""
+    _destroy = "ullm_cuda_event_destroy"
+
+    def query(self) -> int:
+        """abi.EVENT_PENDING / EVENT_SUCCESS; a failed submission raises CudaError with the stored diagnostic."""
+        st = C.c_uint32(0)
+        _call("ullm_cuda_event_query", self._h, C.byref(st))
+        return st.value
+
+    def wait(self, timeout_ms: int = 60000):
+        _call("ullm_cuda_event_wait", self._h, int(timeout_ms))
+
+
+class Prepared(_Handle):
+    """A prepared plan: the ops' metadata copied into the library and their kernels chosen."""
+    _destroy = "ullm_cuda_prepared_destroy"
+
+    def __init__(self, ctx: "Context", ops):
+        super().__init__()
+        arr = (abi.PlanOp * len(ops))(*ops)
+        _call("ullm_cuda_prepare", ctx.handle, arr, len(ops), C.byref(self._h))
+
+    def submit(self, queue: "Queue", bindings, wait=(), want_event: bool = True):
+        arr = (abi.Binding * max(len(bindings), 1))(*bindings)
+        deps = (C.c_void_p * max(len(wait), 1))(*[e.handle for e in wait])
+        ev = Event()
+        _call("ullm_cuda_submit", queue.handle, self._h, arr, len(bindings), deps, len(wait),
+              C.byref(ev._h) if want_event else None)
+        return ev if want_event else None
 
 
 class Comm(_Handle):

@@ -25,6 +25,10 @@ ENCODING_UNQUANTIZED, ENCODING_NVFP4, ENCODING_AQ4, ENCODING_FP8_CHANNEL = 0, 1,
 PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
 EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 KERNEL_AUTO, KERNEL_MATVEC, KERNEL_GEMM = 0, 1, 2
+ACCESS_READ, ACCESS_WRITE, ACCESS_READ_WRITE = 1, 2, 3
+PLAN_OP_HAS_NORM_WEIGHT, PLAN_OP_HAS_RESIDUAL = 1, 2
+SLOT_WEIGHT_VALUES, SLOT_WEIGHT_SCALES, SLOT_INPUT, SLOT_OUTPUT, SLOT_NORM_WEIGHT, SLOT_RESIDUAL = 0, 1, 2, 3, 4, 5
+EVENT_PENDING, EVENT_SUCCESS, EVENT_FAILURE = 0, 1, 2
 STACK_FLAG_NO_GRAPH = 1
 STACK_FLAG_KEEP_ACTIVATIONS = 2
 STACK_FLAG_NCCL_ONLY = 4
@@ -86,6 +90,22 @@ class Slots(C.Structure):
                 ("ranks", u32), ("rank", u32), ("tag", u32), ("gather", u32), ("reserved", u32 * 4)]
 
 
+class PlanOp(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("encoding", u32), ("group_size", u32), ("n", u64), ("k", u64),
+                ("m", u64), ("input_dtype", u32), ("output_dtype", u32), ("prologue", u32), ("epilogue", u32),
+                ("kernel", u32), ("flags", u32), ("rms_eps", C.c_float), ("reserved", u32 * 5)]
+
+
+class Binding(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("op_index", u32), ("slot", u32), ("access", u32),
+                ("reserved0", u32), ("tensor", Tensor), ("reserved", u32 * 4)]
+
+
+class SafetensorsInfo(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("dtype", u32), ("rank", u32), ("rows", u64), ("cols", u64),
+                ("data_offset", u64), ("data_bytes", u64), ("reserved", u32 * 4)]
+
+
 class StackDesc(C.Structure):
     _fields_ = [("struct_size", u32), ("abi_version", u32), ("encoding", u32), ("layers", u32), ("hidden", u32),
                 ("q_heads", u32), ("kv_heads", u32), ("head_dim", u32), ("ffn", u32), ("vocab", u32),
@@ -104,7 +124,7 @@ class StackLinearInfo(C.Structure):
 # sizes pinned in the header's static_asserts
 EXPECTED_SIZES = {
     ErrorSink: 48, VersionInfo: 32, BackendProbeResult: 64, ContextProbeResult: 32, Tensor: 16, Weight: 56,
-    CompletionResult: 56, LinearDesc: 200, StackDesc: 88, StackLinearInfo: 208, Slots: 64,
+    CompletionResult: 56, LinearDesc: 200, StackDesc: 88, StackLinearInfo: 208, Slots: 64, PlanOp: 88, Binding: 56, SafetensorsInfo: 64,
 }
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -149,6 +169,15 @@ SIGNATURES = {
     "ullm_cuda_linear_enqueue": [vp, P(LinearDesc), SINK],
     "ullm_cuda_linear_submit": [vp, P(LinearDesc), P(vp), SINK],
     "ullm_cuda_linear_enqueue_static_scratch": [vp, P(LinearDesc), SINK],
+    "ullm_cuda_safetensors_find": [C.c_char_p, C.c_char_p, P(SafetensorsInfo), SINK],
+    "ullm_cuda_quantize_safetensors": [vp, C.c_char_p, C.c_char_p, P(Weight), SINK],
+    "ullm_cuda_prepare": [vp, P(PlanOp), u32, P(vp), SINK],
+    "ullm_cuda_prepared_destroy": [P(vp), SINK],
+    "ullm_cuda_submit": [vp, vp, P(Binding), u32, P(vp), u32, P(vp), SINK],
+    "ullm_cuda_event_query": [vp, P(u32), SINK],
+    "ullm_cuda_event_wait": [vp, u32, SINK],
+    "ullm_cuda_event_destroy": [P(vp), SINK],
+    "ullm_cuda_context_shutdown": [vp, u32, P(u32), SINK],
     "ullm_cuda_linear_enqueue_partial": [vp, P(LinearDesc), P(Slots), SINK],
     "ullm_cuda_linear_enqueue_reduced": [vp, P(LinearDesc), P(Slots), Tensor, SINK],
     "ullm_cuda_comm_unique_id": [P(C.c_uint8), SINK],
