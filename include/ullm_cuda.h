@@ -80,11 +80,13 @@ typedef uint32_t ullm_status_t;
 
 /* storage encodings, the additive siblings of Encoding::Nvfp4 (dtype.rs:56-66) */
 #define ULLM_CUDA_ENCODING_UNQUANTIZED UINT32_C(0)
-#define ULLM_CUDA_ENCODING_NVFP4 UINT32_C(1) /* descriptor only: every op answers UNSUPPORTED */
+#define ULLM_CUDA_ENCODING_NVFP4 UINT32_C(1) /* u8 [N,K/2] e2m1 pairs + f16 [N,K/16] block scales + one f32 tensor scale;
+                                                quantise / dequantise and the decode linear (M <= 8); no tensor-core path */
 #define ULLM_CUDA_ENCODING_AQ4 UINT32_C(2)   /* u8 [N,K/2] nibbles + f16 [N,K/group] scales */
 #define ULLM_CUDA_ENCODING_FP8_CHANNEL UINT32_C(3) /* e4m3fn [N,K] + f32 [N] scales */
 
 #define ULLM_CUDA_AQ4_GROUP UINT32_C(128)
+#define ULLM_CUDA_NVFP4_BLOCK UINT32_C(16)
 
 /* opaque handles (hip.h:40-46) */
 typedef struct ullm_cuda_context_t ullm_cuda_context_t;
@@ -149,12 +151,13 @@ typedef struct ullm_cuda_tensor_t {
 
 /* A quantised weight W[N,K] (row n = output channel, K contiguous). */
 typedef struct ullm_cuda_weight_t {
-  uint32_t encoding;   /* ULLM_CUDA_ENCODING_AQ4 | ULLM_CUDA_ENCODING_FP8_CHANNEL */
-  uint32_t group_size; /* 128 for AQ4; 0 for FP8_CHANNEL */
+  uint32_t encoding;   /* ULLM_CUDA_ENCODING_AQ4 | ULLM_CUDA_ENCODING_FP8_CHANNEL | ULLM_CUDA_ENCODING_NVFP4 */
+  uint32_t group_size; /* 128 for AQ4; 0 for FP8_CHANNEL; 16 for NVFP4 */
   uint64_t n;
   uint64_t k;
-  ullm_cuda_tensor_t values; /* AQ4: u8 [N,K/2]; FP8: e4m3fn [N,K] */
-  ullm_cuda_tensor_t scales; /* AQ4: f16 [N,K/group]; FP8: f32 [N] */
+  ullm_cuda_tensor_t values; /* AQ4 / NVFP4: u8 [N,K/2]; FP8: e4m3fn [N,K] */
+  ullm_cuda_tensor_t scales; /* AQ4: f16 [N,K/128]; FP8: f32 [N]; NVFP4: f16 [N,K/16], then at the next 16-byte
+                                boundary one f32 tensor scale (16-byte aligned span of that size + 4 bytes) */
 } ullm_cuda_weight_t;
 
 /* ---- version / probe: the CUDA counterparts of hip.h:106-121 ---------------- */

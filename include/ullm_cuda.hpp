@@ -262,7 +262,7 @@ struct QuantLinear {
   ullm_cuda_linear_desc_t desc() const {
     auto d = detail::make_struct<ullm_cuda_linear_desc_t>();
     d.weight.encoding = encoding;
-    d.weight.group_size = encoding == ULLM_CUDA_ENCODING_AQ4 ? ULLM_CUDA_AQ4_GROUP : 0;
+    d.weight.group_size = encoding == ULLM_CUDA_ENCODING_AQ4 ? ULLM_CUDA_AQ4_GROUP : encoding == ULLM_CUDA_ENCODING_NVFP4 ? ULLM_CUDA_NVFP4_BLOCK : 0;
     d.weight.n = n;
     d.weight.k = k;
     d.weight.values = weight_values;

@@ -39,6 +39,16 @@ FP8, per output channel n:
     scale[n] = fp32(amax_n / 448)  (0 if amax 0)
     w8       = e4m3fn_rne(clamp(w / scale, -448, 448)), 0 if scale == 0
     dequant w' = fp32(w8) * scale[n]              (one fp32 rounding)
+NVFP4 (the descriptor the reference defines: crates/ullm-core/src/dtype.rs:56-66, packed 4-bit values with one
+scale per block, scale dtype in {bf16, f16, f32}; its plan adds a tensor scale to the tensor representation and the
+kernel contract: docs/plans/main-plan.md:102-114).  Here: block 16 along K, f16 block scales, one f32 tensor scale.
+    values e2m1 (sign, 2 exponent bits, 1 mantissa bit): magnitudes {0, 0.5, 1, 1.5, 2, 3, 4, 6}
+    ts    = 2^floor(log2(amax_tensor / 6))  (a power of two; 1.0 for an all-zero tensor)
+    sb    = fp16_rne((amax_block / 6) / ts)             (fp32 divisions)
+    code  = 0 if sb == 0 else e2m1_rne(w / (fp32(sb) * ts)), saturating at +-6; ties go to the even code
+    byte j of a row = code[2j] | code[2j+1] << 4
+    layout: packed[N][K/2] u8; scales: f16 [N][K/16], then (at the next 16-byte boundary) the f32 tensor scale
+    dequant w' = e2m1(code) * fp32(sb) * ts             (both products exact in fp32)
 Linear:  y[m,n] = bf16_rne( sum_k fp32(x[m,k]) * w'[n,k] ), fp64 accumulate here.
 """
 
@@ -215,6 +225,71 @@ def fp8_quantize(w: np.ndarray):
 
 def fp8_dequantize(codes: np.ndarray, scale: np.ndarray) -> np.ndarray:
     return (e4m3_decode(codes) * np.ascontiguousarray(scale, np.float32)[:, None]).astype(np.float32)
+
+
+# ---------------------------------------------------------------------------
+# NVFP4
+# ---------------------------------------------------------------------------
+
+NVFP4_BLOCK = 16
+_E2M1_MAG = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32)
+
+
+def e2m1_decode(codes: np.ndarray) -> np.ndarray:
+    c = np.asarray(codes, np.uint8)
+    return np.where(c & 8, -_E2M1_MAG[c & 7], _E2M1_MAG[c & 7]).astype(np.float32)
+
+
+def e2m1_encode(x: np.ndarray) -> np.ndarray:
+    """Round to nearest on the e2m1 grid, ties to the even code, saturating at 6; returns 4-bit codes."""
+    x = np.asarray(x, np.float32)
+    a = np.minimum(np.abs(x), np.float32(6.0))
+    # midpoints between neighbours; at a midpoint the even code (0, 2, 4, 6 -> 0, 1, 2, 4) wins
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+    idx = np.zeros(a.shape, np.uint8)
+    for i, m in enumerate(mids):
+        up = (a > m) | ((a == m) & ((i + 1) % 2 == 0))  # crossing into code i+1: on a tie only if i+1 is even
+        idx = np.where(up, np.uint8(i + 1), idx)
+    sign = (np.signbit(x) & (idx != 0)).astype(np.uint8) << 3  # no negative zero codes
+    return (idx | sign).astype(np.uint8)
+
+
+def nvfp4_scale_bytes(n: int, k: int) -> int:
+    return (n * (k // NVFP4_BLOCK) * 2 + 15) // 16 * 16 + 4
+
+
+def nvfp4_quantize(w: np.ndarray):
+    """fp32 [N,K] (K % 16 == 0) -> (packed u8 [N,K/2], block scales f16 [N,K/16], tensor scale f32 scalar)."""
+    w = np.asarray(w, np.float32)
+    n, k = w.shape
+    assert k % NVFP4_BLOCK == 0
+    amax_t = np.float32(np.abs(w).max()) if w.size else np.float32(0)
+    if amax_t > 0:
+        m, e = np.frexp(np.float32(amax_t / np.float32(6.0)))  # amax/6 = m * 2^e, m in [0.5, 1)
+        ts = np.float32(np.ldexp(np.float32(1.0), int(e) - 1))
+    else:
+        ts = np.float32(1.0)
+    blocks = w.reshape(n, k // NVFP4_BLOCK, NVFP4_BLOCK)
+    amax_b = np.abs(blocks).max(axis=2)
+    sb = ((amax_b / np.float32(6.0)).astype(np.float32) / ts).astype(np.float32).astype(np.float16)
+    step = (sb.astype(np.float32) * ts).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        scaled = (blocks / step[:, :, None]).astype(np.float32)
+    codes = np.where(step[:, :, None] > 0, e2m1_encode(np.nan_to_num(scaled, nan=0.0, posinf=6.0, neginf=-6.0)), np.uint8(0))
+    codes = codes.reshape(n, k).astype(np.uint8)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    return packed, sb, ts
+
+
+def nvfp4_dequantize(packed: np.ndarray, sb: np.ndarray, ts) -> np.ndarray:
+    packed = np.asarray(packed, np.uint8)
+    n, kb = packed.shape
+    codes = np.empty((n, kb * 2), np.uint8)
+    codes[:, 0::2] = packed & 0xF
+    codes[:, 1::2] = packed >> 4
+    v = e2m1_decode(codes).reshape(n, kb * 2 // NVFP4_BLOCK, NVFP4_BLOCK)
+    out = (v * np.asarray(sb, np.float16).astype(np.float32)[:, :, None]).astype(np.float32) * np.float32(ts)
+    return out.astype(np.float32).reshape(n, kb * 2)
 
 
 # ---------------------------------------------------------------------------

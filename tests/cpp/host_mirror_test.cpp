@@ -60,10 +60,13 @@ int main(int argc, char **argv) {
   op.k = 200;  // not a multiple of the group size
   s = Backend::supports(op);
   EXPECT(!s.supported && !s.reason.empty());
-  op.encoding = ULLM_CUDA_ENCODING_NVFP4;
+  op.encoding = ULLM_CUDA_ENCODING_NVFP4;  // served by the decode kernel only: 64 tokens are too many, one is fine
   op.k = 512;
   s = Backend::supports(op);
   EXPECT(!s.supported);
+  op.m = 1;
+  s = Backend::supports(op);
+  EXPECT(s.supported && s.kernel == ULLM_CUDA_KERNEL_MATVEC);
   op.encoding = 77;  // not an encoding at all: an argument error or unsupported, never a crash
   bool handled = false;
   try {

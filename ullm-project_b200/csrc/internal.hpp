@@ -308,6 +308,13 @@ struct LinearArgs {
 
 // returns the number of kernels launched, or -1 after setting *err
 int launch_matvec(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+// NVFP4 (nvfp4.cu): its own decode kernel, quantiser and dequantiser
+bool nvfp4_matvec_supports(const LinearArgs &a, const char **why);
+int launch_matvec_nvfp4(const Context *ctx, cudaStream_t stream, const LinearArgs &a, cudaError_t *err);
+uint64_t nvfp4_scale_bytes(uint64_t n, uint64_t k);
+void launch_nvfp4_quantize(cudaStream_t s, const float *src, uint64_t n, uint64_t k, uint8_t *values, void *scales);
+void launch_nvfp4_dequantize(cudaStream_t s, const uint8_t *values, const void *scales, uint64_t n, uint64_t k, void *out,
+                             uint32_t out_dtype);
 bool matvec_supports(const LinearArgs &a, const char **why);
 
 // `scratch` is the staging memory of the queue whose stream is given (grown on demand, not during capture).

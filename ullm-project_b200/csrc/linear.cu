@@ -56,15 +56,15 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
     a.scales = wp.scales;
   } else {
     // shape-only validation: same rules as resolve_weight, without touching handles
-    if (w.encoding == ULLM_CUDA_ENCODING_NVFP4)
-      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 is a descriptor only; no kernel accepts it");
-    if (w.encoding != ULLM_CUDA_ENCODING_AQ4 && w.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL)
-      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight encoding must be AQ4 or FP8_CHANNEL");
+    if (w.encoding != ULLM_CUDA_ENCODING_AQ4 && w.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL && w.encoding != ULLM_CUDA_ENCODING_NVFP4)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight encoding must be AQ4, FP8_CHANNEL or NVFP4");
     if (w.n == 0 || w.k == 0) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "weight has a zero extent");
     if (w.n > 0x7fffffffULL || w.k > 0x7fffffffULL)
       return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight extents above 2^31-1 are not supported");
     if (w.encoding == ULLM_CUDA_ENCODING_AQ4 && (w.group_size != ULLM_CUDA_AQ4_GROUP || w.k % ULLM_CUDA_AQ4_GROUP))
       return write_error(sink, ULLM_STATUS_UNSUPPORTED, "AQ4 needs group size 128 and K a multiple of 128");
+    if (w.encoding == ULLM_CUDA_ENCODING_NVFP4 && (w.group_size != ULLM_CUDA_NVFP4_BLOCK || w.k % 32))
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 needs block size 16 and K a multiple of 32");
     if (w.encoding == ULLM_CUDA_ENCODING_FP8_CHANNEL && (w.group_size != 0 || w.k % 16))
       return write_error(sink, ULLM_STATUS_UNSUPPORTED, "FP8_CHANNEL needs group_size 0 and K a multiple of 16");
   }
@@ -122,8 +122,12 @@ static ullm_status_t resolve_linear(const ullm_cuda_linear_desc_t *desc, const C
   }
 
   const char *why_mv = "", *why_gemm = "";
-  const bool mv = matvec_supports(a, &why_mv);
-  const bool gm = gemm_supports(a, &why_gemm);
+  const bool nv = a.encoding == ULLM_CUDA_ENCODING_NVFP4;
+  if (nv && (a.norm_weight != nullptr || desc->norm_weight.buffer != nullptr))
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "the NVFP4 decode kernel offers no prologue");
+  const bool mv = nv ? nvfp4_matvec_supports(a, &why_mv) : matvec_supports(a, &why_mv);
+  if (nv) why_gemm = "the tensor-core kernels do not take NVFP4 weights";
+  const bool gm = !nv && gemm_supports(a, &why_gemm);
   uint32_t kernel = desc->kernel;
   if (kernel == ULLM_CUDA_KERNEL_AUTO)
     kernel = (mv && !(gm && auto_prefers_gemm(a))) ? ULLM_CUDA_KERNEL_MATVEC : (gm ? ULLM_CUDA_KERNEL_GEMM : 0u);
@@ -146,8 +150,10 @@ static ullm_status_t enqueue_resolved(Queue *q, const Resolved &r, sink_t *sink)
   ullm_status_t refused = ULLM_STATUS_OK;
   if (!submissions_open(sink, &refused)) return refused;
   cudaError_t e = cudaSuccess;
-  const int launched = r.kernel == ULLM_CUDA_KERNEL_MATVEC ? launch_matvec(q->ctx, q->stream, r.args, &e)
-                                                           : launch_gemm(q->ctx, &q->scratch, q->stream, r.args, &e);
+  const int launched = r.kernel == ULLM_CUDA_KERNEL_MATVEC
+                           ? (r.args.encoding == ULLM_CUDA_ENCODING_NVFP4 ? launch_matvec_nvfp4(q->ctx, q->stream, r.args, &e)
+                                                                          : launch_matvec(q->ctx, q->stream, r.args, &e))
+                           : launch_gemm(q->ctx, &q->scratch, q->stream, r.args, &e);
   if (launched < 0) return cuda_error(sink, e, "linear kernel launch");
   if (launched == 0)
     return write_error(sink, ULLM_STATUS_CUDA_ZERO_DISPATCH, "linear op launched no kernel");

@@ -238,6 +238,10 @@ ullm_status_t ullm_cuda_quantize_safetensors(ullm_cuda_queue_t *queue, const cha
   WeightPtrs wp;
   st = resolve_weight(*weight, q->ctx, sink, &wp);
   if (st != ULLM_STATUS_OK) return st;
+  if (wp.encoding == ULLM_CUDA_ENCODING_NVFP4)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED,
+                       "NVFP4's tensor scale depends on the whole tensor, which this chunked loader never holds: upload the "
+                       "fp32 tensor and use ullm_cuda_quantize");
   Found f;
   st = find_tensor(path, tensor_name, &f, sink);
   if (st != ULLM_STATUS_OK) return st;

@@ -204,7 +204,9 @@ __global__ void fp8_dequantize_kernel(const uint8_t *__restrict__ codes, const f
 
 void launch_quantize(cudaStream_t s, const float *src, uint32_t encoding, uint64_t n, uint64_t k, uint8_t *values,
                      void *scales) {
-  if (encoding == ULLM_CUDA_ENCODING_AQ4) {
+  if (encoding == ULLM_CUDA_ENCODING_NVFP4) {
+    launch_nvfp4_quantize(s, src, n, k, values, scales);
+  } else if (encoding == ULLM_CUDA_ENCODING_AQ4) {
     const uint64_t groups = n * (k / 128);
     aq4_quantize_kernel<<<grid_for(groups * 32, 256), 256, 0, s>>>(src, groups, values, static_cast<__half *>(scales));
   } else {
@@ -219,7 +221,9 @@ void launch_aq4_pack(cudaStream_t s, const int8_t *src, uint64_t bytes, uint8_t 
 }
 void launch_dequantize(cudaStream_t s, uint32_t encoding, const uint8_t *values, const void *scales, uint64_t n,
                        uint64_t k, void *out, uint32_t out_dtype) {
-  if (encoding == ULLM_CUDA_ENCODING_AQ4) {
+  if (encoding == ULLM_CUDA_ENCODING_NVFP4) {
+    launch_nvfp4_dequantize(s, values, scales, n, k, out, out_dtype);
+  } else if (encoding == ULLM_CUDA_ENCODING_AQ4) {
     const uint64_t bytes = n * (k / 2);
     if (out_dtype == ULLM_CUDA_DTYPE_F32)
       aq4_dequantize_kernel<float><<<grid_for(bytes, 256), 256, 0, s>>>(values, static_cast<const __half *>(scales),

@@ -82,15 +82,20 @@ ullm_status_t end_launch(Queue *q, sink_t *sink, const char *what, uint64_t kern
 
 ullm_status_t resolve_weight(const ullm_cuda_weight_t &w, const Context *ctx, sink_t *sink,
                              WeightPtrs *out) noexcept {
-  if (w.encoding == ULLM_CUDA_ENCODING_NVFP4)
-    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 is a descriptor only; no kernel accepts it");
-  if (w.encoding != ULLM_CUDA_ENCODING_AQ4 && w.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL)
-    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight encoding must be AQ4 or FP8_CHANNEL");
+  if (w.encoding != ULLM_CUDA_ENCODING_AQ4 && w.encoding != ULLM_CUDA_ENCODING_FP8_CHANNEL && w.encoding != ULLM_CUDA_ENCODING_NVFP4)
+    return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight encoding must be AQ4, FP8_CHANNEL or NVFP4");
   if (w.n == 0 || w.k == 0) return write_error(sink, ULLM_STATUS_INVALID_ARGUMENT, "weight has a zero extent");
   if (w.n > 0x7fffffffULL || w.k > 0x7fffffffULL)
     return write_error(sink, ULLM_STATUS_UNSUPPORTED, "weight extents above 2^31-1 are not supported");
   uint64_t vbytes, sbytes;
-  if (w.encoding == ULLM_CUDA_ENCODING_AQ4) {
+  if (w.encoding == ULLM_CUDA_ENCODING_NVFP4) {
+    if (w.group_size != ULLM_CUDA_NVFP4_BLOCK)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 block size must be 16");
+    if (w.k % 32 != 0)
+      return write_error(sink, ULLM_STATUS_UNSUPPORTED, "NVFP4 needs K to be a multiple of 32; ragged K is rejected");
+    vbytes = w.n * (w.k / 2);
+    sbytes = nvfp4_scale_bytes(w.n, w.k);
+  } else if (w.encoding == ULLM_CUDA_ENCODING_AQ4) {
     if (w.group_size != ULLM_CUDA_AQ4_GROUP)
       return write_error(sink, ULLM_STATUS_UNSUPPORTED, "AQ4 group size must be 128");
     if (w.k % ULLM_CUDA_AQ4_GROUP != 0)
@@ -108,7 +113,7 @@ ullm_status_t resolve_weight(const ullm_cuda_weight_t &w, const Context *ctx, si
   void *v = nullptr, *s = nullptr;
   ullm_status_t st = resolve(w.values, vbytes, 16, ctx, "weight values", sink, &v);
   if (st != ULLM_STATUS_OK) return st;
-  st = resolve(w.scales, sbytes, 4, ctx, "weight scales", sink, &s);
+  st = resolve(w.scales, sbytes, w.encoding == ULLM_CUDA_ENCODING_NVFP4 ? 16 : 4, ctx, "weight scales", sink, &s);
   if (st != ULLM_STATUS_OK) return st;
   out->values = static_cast<const uint8_t *>(v);
   out->scales = s;

@@ -321,13 +321,16 @@ class Queue(_Handle):
 
 
 def weight_desc(encoding: int, n: int, k: int, values: abi.Tensor, scales: abi.Tensor) -> abi.Weight:
-    return abi.Weight(encoding, 128 if encoding == ENCODING_AQ4 else 0, n, k, values, scales)
+    group = {ENCODING_AQ4: 128, ENCODING_NVFP4: 16}.get(encoding, 0)
+    return abi.Weight(encoding, group, n, k, values, scales)
 
 
 def weight_bytes(encoding: int, n: int, k: int):
     """(values bytes, scales bytes) of a quantised W[N,K]."""
     if encoding == ENCODING_AQ4:
         return n * (k // 2), n * (k // 128) * 2
+    if encoding == ENCODING_NVFP4:  # f16 block scales, then the f32 tensor scale at the next 16-byte boundary
+        return n * (k // 2), (n * (k // 16) * 2 + 15) // 16 * 16 + 4
     return n * k, n * 4
 
 
