@@ -88,6 +88,35 @@ def test_prologues_and_dtypes(gpu, encoding, prologue, x_dtype):
 
 
 @pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("m,n,k,epilogue", [(1, 10240, 1024, U.EPILOGUE_NONE), (1, 14336, 4096, U.EPILOGUE_NONE),
+                                            (1, 9600, 512, U.EPILOGUE_NONE), (1, 9473, 1536, U.EPILOGUE_NONE),
+                                            (2, 5000, 1024, U.EPILOGUE_NONE), (4, 4800, 2560, U.EPILOGUE_NONE),
+                                            (1, 19200, 512, U.EPILOGUE_SWIGLU), (1, 19000, 2048, U.EPILOGUE_SWIGLU)])
+def test_matvec_more_row_groups_than_warps(gpu, encoding, m, n, k, epilogue):
+    """Matrices with a little more than a whole number of rounds of row groups over the GPU's warps: the FP8 kernel
+    cuts the left-over groups into K slices taken by several warps (slices with and without work, odd row counts,
+    the paired rows of the SwiGLU epilogue); the result must not depend on it."""
+    ctx, q = gpu
+    w = o.synth_weights(SEED, 2500 + n + k, n, k)
+    x = o.synth_activations(SEED, 2600 + m + k, m, k)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    wdq = oracle_dequantize(*oracle_quantize(w, encoding), encoding)
+    ref = oracle_linear(x, wdq, epilogue=epilogue)
+    y, res = run_linear(ctx, q, dw, x, kernel=U.KERNEL_MATVEC, epilogue=epilogue)
+    check(y, ref, (encoding, m, n, k))
+    assert res.device_flags == 0 and res.fallback_used == 0
+    if epilogue == U.EPILOGUE_NONE:
+        yf, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_MATVEC, y_dtype=U.DTYPE_F32)
+        ref64 = oracle_linear(x, wdq, out="f64")
+        assert np.abs(yf - ref64).max() <= 2e-5 * (np.abs(ref64).max() + 1e-30)
+        # the same launch twice gives the same bits (fixed summation order across the slices)
+        yf2, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_MATVEC, y_dtype=U.DTYPE_F32)
+        assert np.array_equal(yf.view(np.uint32), yf2.view(np.uint32))
+    assert dw.canaries_intact(q)
+    dw.close()
+
+
+@pytest.mark.parametrize("encoding", ENCODINGS)
 @pytest.mark.parametrize("m,n,k", [(1, 2, 128), (1, 1030, 1024), (2, 514, 512), (4, 256, 1024), (8, 70, 2048)])
 def test_swiglu_epilogue(gpu, encoding, m, n, k):
     """Rows [gate(N/2) | up(N/2)] -> [M, N/2] = bf16(silu(bf16 g) * bf16 u)."""

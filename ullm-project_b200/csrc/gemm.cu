@@ -199,6 +199,61 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// ---- CTA pairs (clusters of two, tcgen05 cta_group::2): rank 0 issues the MMAs for both ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA into this CTA's shared memory, completion on a barrier that may be the pair's other CTA's
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// executed by the same warp of both CTAs of the pair
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrives on one barrier (of either CTA) once every MMA issued so far by this thread has completed in both CTAs
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+// M = 256 over the pair: each CTA supplies its 128 weight rows and its half of the token rows at the same
+// shared-memory offsets, and receives its 128 accumulator lanes of all token columns
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory"); }
 
@@ -214,8 +269,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
 }
 
 // instruction descriptor: D = f32, A = B = e4m3 (format 0), both K-major, M = 128, N = tt
-__host__ __device__ constexpr uint32_t instr_desc_e4m3(int tt) {
-  return (1u << 4) | ((uint32_t)(tt >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc_e4m3(int tt, int rows = BM) {
+  return (1u << 4) | ((uint32_t)(tt >> 3) << 17) | ((uint32_t)(rows >> 4) << 24);
 }
 
 __host__ __device__ constexpr uint32_t tmem_cols(uint32_t want) {
@@ -240,16 +295,19 @@ struct Segment {
 struct Walker {
   uint32_t round = 0, rounds, tiles, kb_all, sk_tile0, sk_ctas;
   uint64_t cur = 0, end = 0, units = 0;
-  __device__ Walker(const GemmParams &p, uint32_t tiles_) {
+  uint32_t me, workers;  // a worker is a CTA, or a CTA pair (both CTAs walk the same sequence)
+  __device__ Walker(const GemmParams &p, uint32_t tiles_, uint32_t me_, uint32_t workers_) {
+    me = me_;
+    workers = workers_;
     kb_all = p.k / BKB;
     tiles = tiles_;
     rounds = p.whole_rounds;
     sk_tile0 = p.sk_tile0;
     sk_ctas = p.sk_ctas;
-    if (blockIdx.x < sk_ctas) {
+    if (me < sk_ctas) {
       units = (uint64_t)(tiles - sk_tile0) * kb_all;
-      cur = start(blockIdx.x);
-      end = start(blockIdx.x + 1);
+      cur = start(me);
+      end = start(me + 1);
     }
   }
   __device__ uint64_t start(uint32_t c) const { return (uint64_t)c * units / sk_ctas; }
@@ -257,9 +315,9 @@ struct Walker {
   __device__ uint32_t owner(uint64_t u) const { return (uint32_t)(((u + 1) * sk_ctas - 1) / units); }
   __device__ bool next(Segment *s) {
     while (round < rounds) {
-      const uint32_t t = round++ * gridDim.x + blockIdx.x;
+      const uint32_t t = round++ * workers + me;
       if (t < sk_tile0) {
-        *s = Segment{t, 0u, kb_all, blockIdx.x, 1u, false};
+        *s = Segment{t, 0u, kb_all, me, 1u, false};
         return true;
       }
     }
@@ -269,14 +327,14 @@ struct Walker {
     const uint64_t left = end - cur;
     s->nkb = kb_all - s->kb0 < left ? kb_all - s->kb0 : (uint32_t)left;
     if (s->nkb == kb_all) {
-      s->first_owner = blockIdx.x;
+      s->first_owner = me;
       s->contributors = 1;
       s->head = false;
     } else {
       const uint64_t t0 = (cur / kb_all) * kb_all;
       s->first_owner = owner(t0);
       s->contributors = owner(t0 + kb_all - 1) - s->first_owner + 1;
-      s->head = blockIdx.x > s->first_owner;
+      s->head = me > s->first_owner;
     }
     cur += s->nkb;
     return true;
@@ -291,16 +349,23 @@ __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
   return r0 + m * 129u;                             // negative: + 1 -> 8 - u, and bit 7
 }
 
-template <uint32_t ENC, int TT, int RT, int KS>
+// PAIR: the kernel is launched in clusters of two CTAs that share every tile: 256 weight rows (128 per CTA) x TT
+// tokens, each CTA loading its own weight rows and HALF of the token rows; rank 0 issues tcgen05.mma.cta_group::2
+// for both, so each SM's tensor core reads half of the activation tile from its own shared memory and the other
+// half from its partner's.  Per flop that is a third less shared-memory traffic than two independent CTAs, which
+// is what bounds the wide FP8 tiles.  No multicast load anywhere: every TMA copy is issued by the CTA it lands in.
+template <uint32_t ENC, int TT, int RT, int KS, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   extern __shared__ uint8_t smem_dyn[];
+  static_assert(!PAIR || (ENC == FP8 && RT == 1 && TT >= 128), "CTA pairs: wide FP8 tiles, one row block per CTA");
   // a stage holds KS bytes of k: a whole k-block, or half of one where the tiles are too large for more
   // than two whole-k-block stages (the loads of a 96 KB stage take longer than its MMAs)
   static_assert(KS == BKB || ENC == FP8, "the AQ4 converters write whole k-blocks");
   constexpr uint32_t SUBS = BKB / KS;                   // stages per k-block
   constexpr uint32_t A_STAGE = (uint32_t)BM * KS;       // one row block of the stage
-  constexpr uint32_t B_BYTES = (uint32_t)TT * KS;       // one activation plane of the stage
+  constexpr uint32_t B_TOK = PAIR ? TT / 2 : TT;        // token rows this CTA loads
+  constexpr uint32_t B_BYTES = B_TOK * KS;              // one activation plane of the stage
   constexpr uint32_t STAGE_BYTES = RT * A_STAGE + 2 * B_BYTES;
   // Up to 64 tokens the two activation planes, adjacent in shared memory, are ONE operand of 2*TT rows: a
   // single MMA per k-slice leaves A.hi in columns [0,TT) and A.lo in [TT,2TT) and the epilogue adds them.
@@ -325,11 +390,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t NS = p.stages, RS = p.raw_stages;
-  const uint32_t tiles_n = (p.n + RT * BM - 1) / (RT * BM), tiles_m = (p.m + TT - 1) / TT;
+  const uint32_t crank = PAIR ? cluster_rank() : 0u;  // 0 issues the pair's MMAs
+  constexpr uint32_t TILE_ROWS = (PAIR ? 2 : RT) * BM;
+  const uint32_t tiles_n = (p.n + TILE_ROWS - 1) / TILE_ROWS, tiles_m = (p.m + TT - 1) / TT;
+  // first weight row of THIS CTA and first token of the tile
   auto tile_origin = [&](uint32_t tile, uint32_t *n0, uint32_t *m0) {
     // m fastest: consecutive tiles share the weight rows (read from HBM once); n fastest: they share the tokens
     const uint32_t tn = p.m_fastest ? tile / tiles_m : tile % tiles_n, tm = p.m_fastest ? tile % tiles_m : tile / tiles_n;
-    *n0 = tn * RT * BM;
+    *n0 = tn * TILE_ROWS + crank * BM;
     *m0 = tm * TT;
   };
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
@@ -358,21 +426,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (uint32_t b = 0; b < 4; ++b) {
       mbar_init(acc_full(b), 1u);                     // tcgen05.commit
-      mbar_init(acc_empty(b), (uint32_t)kEpiWarps);   // one arrival per epilogue warp
+      mbar_init(acc_empty(b), (uint32_t)kEpiWarps * (PAIR ? 2u : 1u));  // one arrival per epilogue warp (of both CTAs)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if (PAIR) {
+    // the partner's barriers must exist before anything signals them, and both CTAs allocate together
+    __syncthreads();
+    cluster_sync_all();
+  }
   if (warp == 1) {
-    tmem_alloc((uint32_t)__cvta_generic_to_shared(&tmem_base_slot), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair((uint32_t)__cvta_generic_to_shared(&tmem_base_slot), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc((uint32_t)__cvta_generic_to_shared(&tmem_base_slot), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const WaitCtl wctl{&abort_flag, p.flags, p.abort_word, p.wait_ns};
-  Walker walk(p, tiles_n * tiles_m);
+  Walker walk(p, tiles_n * tiles_m, PAIR ? blockIdx.x >> 1 : blockIdx.x, PAIR ? gridDim.x >> 1 : gridDim.x);
   Segment sg;
 
   if (warp == 0) {
@@ -392,13 +470,23 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES;
           const int kx = (int)(sg.kb0 * BKB + i * KS);
-          mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_STAGE : 0u) + 2 * B_BYTES);
-          if (ENC == FP8) {
+          if (PAIR) {
+            // both CTAs' bytes complete on rank 0's barrier, which its MMA thread waits for
+            const uint32_t fb = map_to_cta(full(slot), 0u);
+            const int tok0 = (int)(m0 + crank * B_TOK);
+            if (crank == 0) mbar_expect_tx(full(slot), 2u * (A_STAGE + 2 * B_BYTES));
+            tma_load_2d_pair(a_addr, &tmap_w, kx, (int)n0, fb);
+            tma_load_3d_pair(a_addr + A_STAGE, &tmap_x, kx, tok0, 0, fb);
+            tma_load_3d_pair(a_addr + A_STAGE + B_BYTES, &tmap_x, kx, tok0, 1, fb);
+          } else {
+            mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_STAGE : 0u) + 2 * B_BYTES);
+            if (ENC == FP8) {
 #pragma unroll
-            for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_STAGE, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
+              for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_STAGE, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
+            }
+            tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
+            tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
           }
-          tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
-          tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
           if (++slot == NS) {
             slot = 0;
             ++round;
@@ -408,8 +496,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---- MMA issue ------------------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_e4m3((int)MMA_N);
+    if (lane == 0 && crank == 0) {
+      constexpr uint32_t idesc = instr_desc_e4m3((int)MMA_N, PAIR ? 2 * BM : BM);
       constexpr uint32_t idesc_lo = idesc | (1u << 10);  // B operand read as e5m2 (the rest plane of wide tiles)
       uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
@@ -440,11 +528,22 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int k4 = 0; k4 < KS / 32; ++k4) {
               // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
               const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
-              tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-              if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
+              if (PAIR) {
+                tc_mma_pair(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
+                tc_mma_pair(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
+              } else {
+                tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
+                if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
+              }
             }
           }
-          tc_commit(empty(slot));  // the stage may be refilled when these MMAs are done
+          // the stage may be refilled when these MMAs are done (in both CTAs of a pair)
+          if (PAIR) {
+            tc_commit_pair(empty(slot));
+            tc_commit_pair(map_to_cta(empty(slot), 1u));
+          } else {
+            tc_commit(empty(slot));
+          }
           if (ENC == AQ4) {
             if (++in_batch == GB || i + 1 == sg.nkb) {  // a batch does not span tiles
               tc_commit(acc_full(buf));
@@ -452,7 +551,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               in_batch = 0;
             }
           } else if (i + 1 == sg.nkb * SUBS) {
-            tc_commit(acc_full(buf));
+            if (PAIR) {
+              tc_commit_pair(acc_full(buf));
+              tc_commit_pair(map_to_cta(acc_full(buf), 1u));
+            } else {
+              tc_commit(acc_full(buf));
+            }
           }
           if (++slot == NS) {
             slot = 0;
@@ -577,6 +681,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t n0, m0;
       tile_origin(sg.tile, &n0, &m0);
       const bool direct = sg.contributors == 1;
+      // a worker's partials: one pair of slots per CTA (PAIR: the two CTAs of worker w are CTAs 2w and 2w + 1)
+      auto cta_of = [&](uint32_t worker) { return PAIR ? worker * 2u + crank : worker; };
       float *part = direct ? nullptr : p.partial + ((uint64_t)blockIdx.x * 2 + (sg.head ? 0 : 1)) * PART;
       // finished columns c .. c+CH-1 of row block r: final store, or this range's partial
       auto emit = [&](int r, uint32_t c, const float (&v)[CH], bool final_pass) {
@@ -626,7 +732,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty(buf));  // the accumulator may take the segment after next
+          if (lane == 0) {  // the accumulator may take the segment after next
+            if (PAIR)
+              mbar_arrive_cluster(map_to_cta(acc_empty(buf), 0u));
+            else
+              mbar_arrive(acc_empty(buf));
+          }
         }
       } else {
         static_assert(ENC != AQ4 || RT == 1, "the AQ4 epilogue keeps one row block's running sums in registers");
@@ -722,9 +833,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (threadIdx.x == kEpiWarp0 * 32) {
           uint32_t last = 0u;
           if (ok) {
-            const uint32_t prev = atomicAdd(p.tile_counters + (sg.tile - p.sk_tile0), 1u);
+            const uint32_t ci = PAIR ? (sg.tile - p.sk_tile0) * 2u + crank : sg.tile - p.sk_tile0;
+            const uint32_t prev = atomicAdd(p.tile_counters + ci, 1u);
             if (prev + 1 == sg.contributors) {
-              p.tile_counters[sg.tile - p.sk_tile0] = 0u;  // ready for the next launch
+              p.tile_counters[ci] = 0u;  // ready for the next launch
               last = 1u;
             }
           }
@@ -742,7 +854,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               for (int i = 0; i < CH; ++i) f[i] = 0.0f;
               for (uint32_t j = 0; j < sg.contributors; ++j) {
                 // contributor j is range first_owner + j: its tail segment if it began the tile, else its head
-                const float *src = p.partial + ((uint64_t)(sg.first_owner + j) * 2 + (j == 0 ? 1 : 0)) * PART +
+                const float *src = p.partial + ((uint64_t)cta_of(sg.first_owner + j) * 2 + (j == 0 ? 1 : 0)) * PART +
                                    ((uint64_t)r * TT + col0 + c) * BM + row_in_tile;
 #pragma unroll
                 for (int i = 0; i < CH; ++i) f[i] += __ldcg(src + (uint64_t)i * BM);
@@ -762,9 +874,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     // a wait gave up: let copies that may still be in flight land before shared memory is released
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
+  // the partner's MMAs read this CTA's shared memory and signal its barriers: leave together
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR)
+      tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else
+      tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -932,9 +1049,9 @@ bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <uint32_t ENC, int TT, int RT, int KS = BKB>
+template <uint32_t ENC, int TT, int RT, int KS = BKB, bool PAIR = false>
 cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, GemmParams p, uint32_t grid) {
-  constexpr size_t stage = (size_t)RT * BM * KS + 2 * (size_t)TT * KS;
+  constexpr size_t stage = (size_t)RT * BM * KS + 2 * (size_t)(PAIR ? TT / 2 : TT) * KS;
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
   size_t ns = 0, rs = 0;
@@ -950,7 +1067,7 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   p.stages = (uint32_t)ns;
   p.raw_stages = (uint32_t)rs;
   const size_t smem = ns * stage + rs * raw_stage + 1024;
-  auto kern = gemm_kernel<ENC, TT, RT, KS>;
+  auto kern = gemm_kernel<ENC, TT, RT, KS, PAIR>;
   // function attributes are per device: raised once per (device, kernel)
   static std::mutex mu;
   static bool configured[kMaxDevices] = {};
@@ -973,11 +1090,19 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (PAIR) {
+    if (grid % 2 != 0) return cudaErrorInvalidValue;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kern, wmap, xmap, p);
 }
 
@@ -991,6 +1116,9 @@ int env_int(const char *name) {
 #else
 constexpr int env_int(const char *) { return 0; }
 #endif
+
+// CTA pairs for wide FP8 tiles unless a tuning build says otherwise
+constexpr bool kPairsByDefault = true;
 
 int tile_tokens(uint32_t m, uint32_t enc) {
   static const int forced = env_int("ULLM_CUDA_GEMM_TOKENS");
@@ -1006,6 +1134,7 @@ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 // Where everything lives in the scratch area, and how the problem is cut up.
 struct Plan {
   int tt = 0, rt = 1;
+  bool cta_pairs = false;  // clusters of two CTAs share 256-row tiles (tcgen05 cta_group::2)
   uint32_t tiles = 0, grid = 0, whole_rounds = 0, sk_tile0 = 0, sk_ctas = 0;
   bool m_fastest = false;
   size_t off_planes = 0, off_tok = 0, off_pair = 0, off_partial = 0, bytes = 0;
@@ -1027,33 +1156,43 @@ Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
     pl.rt = (a.k >= 8192 && tiles2 >= sms) ? 2 : 1;
     if (forced_rows == 128) pl.rt = 1;
     if (forced_rows == 256) pl.rt = 2;
+    // CTA pairs wherever the second CTA of a pair has rows of its own
+    static const int forced_pairs = env_int("ULLM_CUDA_GEMM_PAIRS");
+    pl.cta_pairs = kPairsByDefault && sms % 2 == 0 && a.n > (uint32_t)BM;
+    if (forced_pairs == 1) pl.cta_pairs = sms % 2 == 0;
+    if (forced_pairs == 2) pl.cta_pairs = false;
+    if (pl.cta_pairs) pl.rt = 1;
   }
-  const uint32_t tiles_n = (a.n + pl.rt * BM - 1) / (pl.rt * BM);
+  // workers walk the tiles: CTAs, or CTA pairs with 256-row tiles
+  const uint32_t per_worker = pl.cta_pairs ? 2u : 1u;
+  const uint32_t workers = sms / per_worker;
+  const uint32_t tile_rows = (pl.cta_pairs ? 2 : pl.rt) * BM;
+  const uint32_t tiles_n = (a.n + tile_rows - 1) / tile_rows;
   const uint32_t kb = a.k / BKB;
   pl.tiles = tiles_n * tiles_m;
-  uint32_t grid = pl.tiles < sms ? pl.tiles : sms;
+  uint32_t grid = pl.tiles < workers ? pl.tiles : workers;
   // Whole tiles only: ceil(tiles / grid) rounds.  Hybrid: the full rounds whole, the remaining tiles cut
-  // along K over the CTAs, which costs each CTA up to two partial tiles (written, fenced, read back).
+  // along K over the workers, which costs each CTA up to two partial tiles (written, fenced, read back).
   // Costs in k-block times; a partial of 128 x 256 fp32 is worth about five of them.
   static const int forced_whole = env_int("ULLM_CUDA_GEMM_WHOLE");
-  const uint32_t full = pl.tiles / sms, rem = pl.tiles % sms;
+  const uint32_t full = pl.tiles / workers, rem = pl.tiles % workers;
   const double part = 5.0 * pl.rt * pl.tt / 256.0;
-  const double cost_whole = (double)((pl.tiles + sms - 1) / sms) * kb;
-  const double cost_hybrid = (double)full * kb + (rem ? (double)rem * kb / sms + 2.0 * part : 0.0);
+  const double cost_whole = (double)((pl.tiles + workers - 1) / workers) * kb;
+  const double cost_hybrid = (double)full * kb + (rem ? (double)rem * kb / workers + 2.0 * part : 0.0);
   const bool hybrid = allow_partials && rem != 0 && (uint64_t)rem * kb >= 8 && forced_whole != 1 &&
                       (forced_whole == 2 || cost_hybrid < cost_whole);
   if (hybrid) {
-    grid = sms;
+    grid = workers;
     pl.whole_rounds = full;
-    pl.sk_tile0 = full * sms;
-    uint64_t ctas = (uint64_t)rem * kb / 4;  // at least four k-blocks per range
-    pl.sk_ctas = (uint32_t)(ctas > sms ? sms : ctas);
+    pl.sk_tile0 = full * workers;
+    uint64_t ranges = (uint64_t)rem * kb / 4;  // at least four k-blocks per range
+    pl.sk_ctas = (uint32_t)(ranges > workers ? workers : ranges);
   } else {
     pl.whole_rounds = (pl.tiles + grid - 1) / grid;
     pl.sk_tile0 = pl.tiles;
     pl.sk_ctas = 0;
   }
-  pl.grid = grid;
+  pl.grid = grid * per_worker;
   pl.m_fastest = (uint64_t)2 * a.m * a.k <= (uint64_t)96 << 20;  // the activation planes stay in L2
   size_t off = 0;
   pl.off_planes = off;
@@ -1063,7 +1202,7 @@ Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
   pl.off_pair = off;
   if (a.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU) off += align256((size_t)a.m * a.n * 2);
   pl.off_partial = off;
-  if (pl.sk_ctas != 0) off += align256((size_t)pl.sk_ctas * 2 * pl.rt * pl.tt * BM * 4);
+  if (pl.sk_ctas != 0) off += align256((size_t)pl.sk_ctas * per_worker * 2 * pl.rt * pl.tt * BM * 4);
   pl.bytes = off;
   return pl;
 }
@@ -1122,8 +1261,10 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   }
   CUtensorMap wmap, xmap;
   static const bool whole_k_stage = env_int("ULLM_CUDA_GEMM_STAGE_K") == 128;
-  const uint32_t ks = (a.encoding == FP8 && pl.tt == 256 && !whole_k_stage) ? 64u : 128u;
-  if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding, ks) || !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)pl.tt, ks))
+  const uint32_t ks = (a.encoding == FP8 && pl.tt == 256 && (pl.cta_pairs || !whole_k_stage)) ? 64u : 128u;
+  // a CTA of a pair loads half of the tile's tokens
+  if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding, ks) ||
+      !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)(pl.cta_pairs ? pl.tt / 2 : pl.tt), ks))
     return cudaErrorInvalidValue;
   if (a.encoding == AQ4) {
     switch (pl.tt) {
@@ -1139,7 +1280,9 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
       case 64: e = launch_tile<FP8, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
       case 128: e = launch_tile<FP8, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
       default:
-        if (ks == 64)
+        if (pl.cta_pairs)
+          e = launch_tile<FP8, 256, 1, 64, true>(stream, wmap, xmap, p, pl.grid);
+        else if (ks == 64)
           e = pl.rt == 2 ? launch_tile<FP8, 256, 2, 64>(stream, wmap, xmap, p, pl.grid)
                          : launch_tile<FP8, 256, 1, 64>(stream, wmap, xmap, p, pl.grid);
         else

@@ -94,6 +94,7 @@ struct Params {
   float rms_eps;
   uint32_t k_pad;   // K rounded up to a whole warp iteration
   uint32_t vec_ok;  // activation rows allow 16-byte loads
+  uint32_t tail_slices;  // > 1: the row groups left after the whole rounds are cut into this many K slices
   const void *norm_weight;  // bf16 gamma[K] of the RMSNorm prologue, or null
   const float *residual;    // f32 [M, res_stride] added to the result, or null
   uint64_t res_stride;
@@ -579,6 +580,8 @@ template <int M, int R, int U, uint32_t ENC, int T, int MODE, int S = 1>
 __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   static_assert(S == 1 || (ENC == FP8 && (T / 32) % S == 0 && (T / 32) / S <= 15), "K slices: FP8 only, one named barrier per warp set");
+  // S == 1, FP8: the row groups that do not fill a whole round over all warps may be cut into K slices at run time
+  constexpr bool kTail = S == 1 && ENC == FP8;
   constexpr int E = Piece<ENC>::kElems;
   constexpr int CACHE = M <= 2 ? 4 : 2;
   constexpr bool IN = MODE == kModePushIn || MODE == kModePushInCluster;
@@ -593,8 +596,9 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   const uint32_t groups = pair ? (half_n + R / 2 - 1) / (R / 2 > 0 ? R / 2 : 1) : (p.n + R - 1) / R;
   const uint32_t iters = p.k_pad / (E * 32);
   const uint32_t it_per = (iters + S - 1) / S;
-  const uint32_t it_begin = slice * it_per;
-  const uint32_t it_end = it_begin + it_per < iters ? it_begin + it_per : iters;
+  uint32_t slice_cur = slice, slices_cur = S;  // of the row group in hand
+  uint32_t it_begin = slice * it_per;
+  uint32_t it_end = it_begin + it_per < iters ? it_begin + it_per : iters;
   const uint32_t pieces = p.k_pad / 32;
   const uint64_t row_bytes = ENC == AQ4 ? p.k / 2 : p.k;
   // weight row of slot r in group g (>= n when out of range)
@@ -671,14 +675,33 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   }
   // after the block-reduction words: partial sums of the K slices, then the cluster gather's arrays
   float *slice_part = red + M * kMaxWarps;                                  // [2][T/32][R*M] when S > 1
-  float *ss_parts = slice_part + (S > 1 ? 2 * (T / 32) * R * M : 0);        // [M][kMaxClusterBlocks]
+  float *ss_parts = slice_part + (S > 1 || kTail ? 2 * (T / 32) * R * M : 0);  // [M][kMaxClusterBlocks]
   uint32_t *gathered = reinterpret_cast<uint32_t *>(ss_parts + M * kMaxClusterBlocks);  // packed bf16 [M][K], 16-byte aligned
   (void)IN;
   stage_activations<M, T, CACHE, ENC, MODE>(p, xs, aq, red, gathered, ss_parts);
 
   bool prefetched = true;
   uint32_t parity = 0;
-  for (uint32_t g = gwarp; g < groups; g += nwarps) {
+  // Whole rounds: one row group per warp (set) and round.  What is left over (fewer groups than warps) would
+  // keep a few warps streaming whole rows while the others idle; with tail_slices > 1 each left-over group is
+  // taken by that many consecutive warps, spread over all blocks, each with a slice of K.
+  const uint32_t tail = kTail ? p.tail_slices : 1u;
+  const uint32_t whole = tail > 1u ? groups / nwarps * nwarps : groups;
+  bool in_tail = false;
+  for (uint32_t g = gwarp;; g += nwarps) {
+    if (g >= whole) {
+      if (!kTail || tail <= 1u || in_tail) break;
+      in_tail = true;
+      const uint32_t li = (warp / tail) * gridDim.x + blockIdx.x;
+      if (li >= groups - whole) break;  // the same answer in every warp of a set
+      g = whole + li;
+      slices_cur = tail;
+      slice_cur = warp % tail;
+      const uint32_t per = (iters + tail - 1) / tail;
+      it_begin = slice_cur * per;
+      it_end = it_begin + per < iters ? it_begin + per : iters;
+      if (it_begin > it_end) it_begin = it_end;
+    }
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -784,8 +807,8 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         acc[r][m] = v;
       }
-    if (S > 1) {
-      // the S slices of this row group meet in shared memory; slice 0 adds them in slice order.  The buffers
+    if (S > 1 || (kTail && slices_cur > 1u)) {
+      // the slices of this row group meet in shared memory; slice 0 adds them in slice order.  The buffers
       // alternate, so a warp that runs ahead writes the other buffer and then stops at the next barrier.
       float *mine = slice_part + ((uint64_t)parity * (T / 32) + warp) * (R * M);
       if (lane == 0) {
@@ -794,9 +817,9 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
 #pragma unroll
           for (int m = 0; m < M; ++m) mine[r * M + m] = acc[r][m];
       }
-      asm volatile("bar.sync %0, %1;" ::"r"(1u + warp / S), "n"(S * 32) : "memory");
-      if (slice == 0 && lane == 0) {
-        for (int sl = 1; sl < S; ++sl)
+      asm volatile("bar.sync %0, %1;" ::"r"(1u + warp / slices_cur), "r"(slices_cur * 32u) : "memory");
+      if (slice_cur == 0 && lane == 0) {
+        for (uint32_t sl = 1; sl < slices_cur; ++sl)
 #pragma unroll
           for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -804,7 +827,7 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
       }
       parity ^= 1u;
     }
-    if (lane == 0 && slice == 0) {
+    if (lane == 0 && slice_cur == 0) {
       if (ENC == FP8) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -905,11 +928,23 @@ int pick_cluster(Kern kern, int sm_count, int threads, size_t smem, int *blocks_
   return 0;
 }
 
+// K slices for the row groups left after the whole rounds (1 = none): the largest of 8, 4, 2 that divides the
+// warps of a block, leaves at most 15 warp sets per block (one named barrier each) and finds a warp set for every
+// left-over group.
+inline uint32_t tail_slices(uint32_t groups, uint32_t warps, uint32_t warps_per_block) {
+  if (warps == 0 || groups < warps) return 1u;
+  const uint32_t left = groups % warps;
+  if (left == 0) return 1u;
+  for (uint32_t s = 8; s >= 2; s /= 2)
+    if (warps_per_block % s == 0 && warps_per_block / s <= 15 && (uint64_t)left * s <= warps) return s;
+  return 1u;
+}
+
 template <int M, int R, int U, uint32_t ENC, int T, int S = 1>
 cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p_in) {
   Params p = p_in;
   const bool want_cluster = p.pi.tp != 0 && p.pi.cluster != 0;
-  constexpr size_t slice_floats = S > 1 ? (size_t)2 * (T / 32) * R * M : 0;
+  constexpr size_t slice_floats = S > 1 || (S == 1 && ENC == FP8) ? (size_t)2 * (T / 32) * R * M : 0;
   const int mode = p.pi.tp != 0 ? (want_cluster ? kModePushInCluster : kModePushIn) : (p.po.tp != 0 ? kModePushOut : kModePlain);
   const size_t smem = smem_bytes(M, p.k_pad, ENC, p.k, mode == kModePushInCluster, slice_floats);
   if (mode == kModePushInCluster && (smem > kSmemBudget || p.prologue == ULLM_CUDA_PROLOGUE_SWIGLU || p.k % 8 != 0)) {
@@ -977,14 +1012,21 @@ cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p_
     attr[1].val.clusterDim.z = 1;
     cfg.numAttrs = 2;
   }
+  p.tail_slices = S == 1 && ENC == FP8 ? tail_slices(groups, grid * (uint32_t)(T / 32), T / 32) : 1u;
   cfg.gridDim = dim3(grid);
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 // Share of the last round of row groups that is filled: 1.0 = every warp gets the same work.
-inline double balance(uint32_t units, uint32_t warps) {
+inline double balance(uint32_t units, uint32_t warps, uint32_t warps_per_block = 0) {
   const uint32_t rounds = (units + warps - 1) / warps;
-  return rounds == 0 ? 0.0 : (double)units / ((double)rounds * warps);
+  if (rounds == 0) return 0.0;
+  double cost = (double)rounds;
+  if (warps_per_block != 0) {  // the last round may be cut into K slices
+    const uint32_t s = tail_slices(units, warps, warps_per_block);
+    if (s > 1) cost = (double)(units / warps) + 1.0 / s;
+  }
+  return (double)units / (cost * warps);
 }
 
 #ifdef ULLM_CUDA_TUNING
@@ -1010,9 +1052,10 @@ cudaError_t launch_m1(const Context *ctx, cudaStream_t stream, const Params &p) 
     // Measured on B200 (HBM GB/s over 7 decode shapes and a whole stack): the two best
     // configurations are 4 rows x 2 loads on 640 threads and 2 rows x 4 loads on 1024 threads;
     // which one wins on a shape follows from how evenly the row groups divide among the warps.
-    const double b4 = balance(pair ? (rows + 1) / 2 : (rows + 3) / 4, (uint32_t)ctx->sm_count * 20u);
-    const double b2 = balance(pair ? rows : (rows + 1) / 2, (uint32_t)ctx->sm_count * 32u);
-    const double b1 = pair ? 0.0 : balance(rows, (uint32_t)ctx->sm_count * 32u);
+    const uint32_t tb = ENC == FP8 ? 1u : 0u;  // FP8 cuts the last round into K slices
+    const double b4 = balance(pair ? (rows + 1) / 2 : (rows + 3) / 4, (uint32_t)ctx->sm_count * 20u, 20u * tb);
+    const double b2 = balance(pair ? rows : (rows + 1) / 2, (uint32_t)ctx->sm_count * 32u, 32u * tb);
+    const double b1 = pair ? 0.0 : balance(rows, (uint32_t)ctx->sm_count * 32u, 32u * tb);
     v = b2 >= b4 ? 8 : 9;
     if (b1 > (b2 > b4 ? b2 : b4) + 0.25) v = 4;  // few, long rows: one row per pass
     if (ENC == FP8 && !pair && p.k >= 2048u) {
@@ -1060,8 +1103,9 @@ cudaError_t launch_m(const Context *ctx, cudaStream_t stream, const Params &p) {
     const bool pair = p.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
     const uint32_t rows = pair ? p.n / 2 : p.n;
     const uint32_t warps = (uint32_t)ctx->sm_count * (T / 32);
-    const double b2 = balance(pair ? rows : (rows + 1) / 2, warps);
-    const double b1 = pair ? 0.0 : balance(rows, warps);
+    const uint32_t tb = ENC == FP8 ? (uint32_t)(T / 32) : 0u;
+    const double b2 = balance(pair ? rows : (rows + 1) / 2, warps, tb);
+    const double b1 = pair ? 0.0 : balance(rows, warps, tb);
     if (b2 >= b1 - 0.05) return launch_one<M, 2, 2, ENC, T>(ctx, stream, p);
     return launch_one<M, 1, 4, ENC, T>(ctx, stream, p);
   }
