@@ -51,6 +51,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace ullm {
@@ -88,7 +89,25 @@ struct GemmParams {
   uint64_t wait_ns;         // limit of one barrier wait
   const float *residual;    // f32 [m, res_stride] added to the result, or null
   uint64_t res_stride;
+  uint32_t out_bufs;        // > 0: bf16 results leave through shared memory and TMA stores, this many 2 KiB slots per epilogue warp
+#ifdef ULLM_CUDA_TUNING
+  unsigned long long *stats;  // tuning builds: clocks the single-thread roles spent waiting, summed over CTAs
+  uint32_t dbg;               // timing experiments (results are wrong): 1 = rest plane read as e4m3, 2 = rest plane skipped,
+                              // 4 = activation planes not loaded, 8 = no MMA issued, 16 = weights not loaded,
+                              // 32 = nothing stored, 64 = accumulators not read, 128 = plain arrive instead of commit
+#endif
 };
+
+#ifdef ULLM_CUDA_TUNING
+#define GEMM_STAT_DECL unsigned long long st_wait_a = 0, st_wait_b = 0; const long long st_t0 = clock64();
+#define GEMM_STAT_WAIT(var, expr) do { const long long t_ = clock64(); expr; var += (unsigned long long)(clock64() - t_); } while (0)
+#define GEMM_STAT_FLUSH(base) do { if (p.stats != nullptr) { atomicAdd(p.stats + (base), (unsigned long long)(clock64() - st_t0)); \
+  atomicAdd(p.stats + (base) + 1, st_wait_a); atomicAdd(p.stats + (base) + 2, st_wait_b); } } while (0)
+#else
+#define GEMM_STAT_DECL
+#define GEMM_STAT_WAIT(var, expr) do { expr; } while (0)
+#define GEMM_STAT_FLUSH(base) do { } while (0)
+#endif
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -199,6 +218,18 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// TMA store of a [rows x tokens] box from shared memory; bulk-group bookkeeping of the issuing thread
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {  // at most N groups still read their shared-memory source
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- CTA pairs (clusters of two, tcgen05 cta_group::2): rank 0 issues the MMAs for both ----
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -356,7 +387,8 @@ __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
 // is what bounds the wide FP8 tiles.  No multicast load anywhere: every TMA copy is issued by the CTA it lands in.
 template <uint32_t ENC, int TT, int RT, int KS, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                const __grid_constant__ CUtensorMap tmap_y, const GemmParams p) {
   extern __shared__ uint8_t smem_dyn[];
   static_assert(!PAIR || (ENC == FP8 && RT == 1 && TT >= 128), "CTA pairs: wide FP8 tiles, one row block per CTA");
   // a stage holds KS bytes of k: a whole k-block, or half of one where the tiles are too large for more
@@ -403,6 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
   const uint32_t smem0 = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
   const uint32_t raw0 = smem0 + NS * STAGE_BYTES;
+  const uint32_t out0 = raw0 + RS * RT * RAW_BYTES;  // epilogue staging: [warp][slot][32 tokens][32 rows] bf16
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
   auto full = [&](uint32_t s) { return bar0 + s * 8u; };                          // TMA bytes of the stage landed
   auto a_full = [&](uint32_t s) { return bar0 + (MAX_STAGES + s) * 8u; };         // AQ4: operand tile converted
@@ -460,11 +493,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t slot = 0, round = 0;
       bool ok = true;
+      GEMM_STAT_DECL
       while (ok && walk.next(&sg)) {
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
         for (uint32_t i = 0; i < sg.nkb * SUBS; ++i) {
-          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, wctl)) {
+          bool got = true;
+          if (round > 0) GEMM_STAT_WAIT(st_wait_a, got = mbar_wait(empty(slot), (round - 1) & 1u, wctl));
+          if (!got) {
             ok = false;
             break;
           }
@@ -474,18 +510,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             // both CTAs' bytes complete on rank 0's barrier, which its MMA thread waits for
             const uint32_t fb = map_to_cta(full(slot), 0u);
             const int tok0 = (int)(m0 + crank * B_TOK);
-            if (crank == 0) mbar_expect_tx(full(slot), 2u * (A_STAGE + 2 * B_BYTES));
-            tma_load_2d_pair(a_addr, &tmap_w, kx, (int)n0, fb);
-            tma_load_3d_pair(a_addr + A_STAGE, &tmap_x, kx, tok0, 0, fb);
-            tma_load_3d_pair(a_addr + A_STAGE + B_BYTES, &tmap_x, kx, tok0, 1, fb);
+#ifdef ULLM_CUDA_TUNING
+            const bool no_x = (p.dbg & 4u) != 0u, no_w = (p.dbg & 16u) != 0u;
+#else
+            constexpr bool no_x = false, no_w = false;
+#endif
+            if (crank == 0) mbar_expect_tx(full(slot), 2u * ((no_w ? 0u : A_STAGE) + (no_x ? 0u : 2 * B_BYTES)));
+            if (!no_w) tma_load_2d_pair(a_addr, &tmap_w, kx, (int)n0, fb);
+            if (!no_x) {
+              tma_load_3d_pair(a_addr + A_STAGE, &tmap_x, kx, tok0, 0, fb);
+              tma_load_3d_pair(a_addr + A_STAGE + B_BYTES, &tmap_x, kx, tok0, 1, fb);
+            }
           } else {
-            mbar_expect_tx(full(slot), (ENC == FP8 ? RT * A_STAGE : 0u) + 2 * B_BYTES);
-            if (ENC == FP8) {
+#ifdef ULLM_CUDA_TUNING
+            const bool no_x = (p.dbg & 4u) != 0u, no_w = (p.dbg & 16u) != 0u;
+#else
+            constexpr bool no_x = false, no_w = false;
+#endif
+            mbar_expect_tx(full(slot), ((ENC == FP8 && !no_w) ? RT * A_STAGE : 0u) + (no_x ? 0u : 2 * B_BYTES));
+            if (ENC == FP8 && !no_w) {
 #pragma unroll
               for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_STAGE, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
             }
-            tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
-            tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
+            if (!no_x) {
+              tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
+              tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
+            }
           }
           if (++slot == NS) {
             slot = 0;
@@ -493,6 +543,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      GEMM_STAT_FLUSH(0);
     }
   } else if (warp == 1) {
     // ---- MMA issue ------------------------------------------------------------------------
@@ -501,12 +552,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_lo = idesc | (1u << 10);  // B operand read as e5m2 (the rest plane of wide tiles)
       uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
+#ifdef ULLM_CUDA_TUNING
+      const uint32_t id_lo = (p.dbg & 1u) ? idesc : idesc_lo;
+      const bool skip_lo = (p.dbg & 2u) != 0u, skip_mma = (p.dbg & 8u) != 0u;
+#else
+      constexpr uint32_t id_lo = idesc_lo;
+      constexpr bool skip_lo = false, skip_mma = false;
+#endif
+      GEMM_STAT_DECL
       while (ok && walk.next(&sg)) {
         uint32_t buf = 0;
         if (ENC == FP8) {
           buf = seg % NB;
           const uint32_t use = seg / NB;
-          if (use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl);
+          if (use >= 1) GEMM_STAT_WAIT(st_wait_b, ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl));
         }
         for (uint32_t i = 0; i < sg.nkb * SUBS && ok; ++i) {
           uint32_t fresh = i == 0 ? 1u : 0u;
@@ -517,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl);
             ok = ok && mbar_wait(a_full(slot), round & 1u, wctl);
           }
-          ok = ok && mbar_wait(full(slot), round & 1u, wctl);
+          GEMM_STAT_WAIT(st_wait_a, ok = ok && mbar_wait(full(slot), round & 1u, wctl));
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
@@ -528,16 +587,22 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int k4 = 0; k4 < KS / 32; ++k4) {
               // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
               const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
+              if (skip_mma) continue;
               if (PAIR) {
                 tc_mma_pair(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-                tc_mma_pair(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
+                if (!skip_lo) tc_mma_pair(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
               } else {
                 tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-                if (!NCAT) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), idesc_lo, 1u);
+                if (!NCAT && !skip_lo) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
               }
             }
           }
           // the stage may be refilled when these MMAs are done (in both CTAs of a pair)
+#ifdef ULLM_CUDA_TUNING
+          if ((p.dbg & 128u) != 0u && !PAIR) {
+            mbar_arrive(empty(slot));
+          } else
+#endif
           if (PAIR) {
             tc_commit_pair(empty(slot));
             tc_commit_pair(map_to_cta(empty(slot), 1u));
@@ -565,6 +630,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ++seg;
       }
+      GEMM_STAT_FLUSH(3);
     }
   } else if (warp == 2) {
     // ---- AQ4: TMA of the packed nibble tiles (weights: nothing to wait for) ------------------
@@ -675,8 +741,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t row_in_tile = quarter * 32 + lane;
     const float mult = ENC == AQ4 ? 512.0f : 1.0f;  // 2^9: the nibble bytes were read as u * 2^-9
     constexpr uint64_t PART = (uint64_t)RT * TT * BM;  // floats of one partial tile
-    uint32_t seg = 0, batch = 0;
+    uint32_t seg = 0, batch = 0, out_n = 0;
     bool ok = true;
+    GEMM_STAT_DECL
     while (walk.next(&sg)) {
       uint32_t n0, m0;
       tile_origin(sg.tile, &n0, &m0);
@@ -693,6 +760,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         const uint32_t row = n0 + r * BM + row_in_tile;
         if (row >= p.n) return;
+#ifdef ULLM_CUDA_TUNING
+        if ((p.dbg & 32u) != 0u && v[0] != 1234.5f) return;
+#endif
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
           const uint32_t tok = m0 + c + i;
@@ -708,10 +778,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       if (ENC == FP8) {
         const uint32_t buf = seg % NB, use = seg / NB;
-        ok = ok && mbar_wait(acc_full(buf), use & 1u, wctl);
+        GEMM_STAT_WAIT(st_wait_a, ok = ok && mbar_wait(acc_full(buf), use & 1u, wctl));
         if (ok) {
           tc_fence_after();
-          if (active) {
+#ifdef ULLM_CUDA_TUNING
+          const bool skip_read = (p.dbg & 64u) != 0u;
+#else
+          constexpr bool skip_read = false;
+#endif
+          if (active && !skip_read) {
 #pragma unroll 1
             for (int r = 0; r < RT; ++r) {
               const uint32_t row = n0 + r * BM + row_in_tile;
@@ -726,7 +801,37 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
                   f[i] = (NCAT ? fmaf(__uint_as_float(v2[i]), 0.0625f, __uint_as_float(v[i])) : __uint_as_float(v[i])) * sc;
-                emit(r, col0 + c, f, direct);
+                if (CH == 32 && p.out_bufs != 0u && direct) {
+                  // bf16 results: this warp's 32 rows x 32 tokens go to its own shared-memory slot and leave by one
+                  // TMA store (clipped at the matrix edges), so the stores cost the warp 32 shared-memory writes
+                  const uint32_t slot_addr = out0 + ((e * p.out_bufs + (out_n % p.out_bufs)) << 11);
+                  if (lane == 0) {
+                    if (p.out_bufs > 1u)
+                      bulk_wait_read<1>();
+                    else
+                      bulk_wait_read<0>();
+                  }
+                  __syncwarp();
+#pragma unroll
+                  for (int i = 0; i < CH; ++i) {
+                    const uint32_t tok = m0 + col0 + c + i;
+                    float o = f[i] * (mult * __ldg(p.tok_scale + (tok < p.m ? tok : 0u)));
+                    if (p.residual != nullptr && tok < p.m && row < p.n) o += p.residual[(uint64_t)tok * p.res_stride + row];
+                    const __nv_bfloat16 h = __float2bfloat16_rn(o);
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(slot_addr + (uint32_t)i * 64u + lane * 2u),
+                                 "h"(*reinterpret_cast<const unsigned short *>(&h))
+                                 : "memory");
+                  }
+                  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                  __syncwarp();
+                  if (lane == 0) {
+                    tma_store_2d(&tmap_y, slot_addr, (int)(n0 + r * BM + quarter * 32u), (int)(m0 + col0 + c));
+                    bulk_commit();
+                  }
+                  ++out_n;
+                } else {
+                  emit(r, col0 + c, f, direct);
+                }
               }
             }
           }
@@ -867,6 +972,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ++seg;
     }
+    if (lane == 0 && p.out_bufs != 0u) bulk_wait_all();  // the stores have read their slots and are on their way
+#ifdef ULLM_CUDA_TUNING
+    if (threadIdx.x == kEpiWarp0 * 32) GEMM_STAT_FLUSH(6);
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -1049,8 +1158,22 @@ bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bf16 output [m][y_stride]: box = 32 channels x 32 tokens (one epilogue warp's piece), no swizzle, clipped at the edges
+bool make_y_map(CUtensorMap *map, const void *y, uint32_t m, uint32_t n, uint64_t y_stride) {
+  EncodeTiled enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {n, m};
+  const cuuint64_t strides[1] = {y_stride * 2};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(y), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <uint32_t ENC, int TT, int RT, int KS = BKB, bool PAIR = false>
-cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, GemmParams p, uint32_t grid) {
+cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, const CUtensorMap *ymap,
+                        GemmParams p, uint32_t grid) {
   constexpr size_t stage = (size_t)RT * BM * KS + 2 * (size_t)(PAIR ? TT / 2 : TT) * KS;
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
@@ -1064,9 +1187,25 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
     ns = budget / stage;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
   }
+  // staging for the TMA stores of the epilogue (wide FP8 tiles, bf16 output): two 2 KiB slots per epilogue warp
+  // if they fit beside the stages, else one; a stage is given up only if not even that fits
+  size_t out_bytes = 0;
+  p.out_bufs = 0;
+  if (ENC == FP8 && TT >= 128 && ymap != nullptr) {
+    constexpr size_t one = (size_t)kEpiWarps * 2048;
+    if (ns * stage + 2 * one <= budget) {
+      p.out_bufs = 2;
+    } else if (ns * stage + one <= budget) {
+      p.out_bufs = 1;
+    } else if (ns > 2) {
+      --ns;
+      p.out_bufs = ns * stage + 2 * one <= budget ? 2 : 1;
+    }
+    out_bytes = p.out_bufs * one;
+  }
   p.stages = (uint32_t)ns;
   p.raw_stages = (uint32_t)rs;
-  const size_t smem = ns * stage + rs * raw_stage + 1024;
+  const size_t smem = ns * stage + rs * raw_stage + out_bytes + 1024;
   auto kern = gemm_kernel<ENC, TT, RT, KS, PAIR>;
   // function attributes are per device: raised once per (device, kernel)
   static std::mutex mu;
@@ -1077,8 +1216,8 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> g(mu);
-    if (!configured[dev]) {
-      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!configured[dev]) {  // the largest size any launch of this instantiation asks for
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(budget + 1024));
       if (e != cudaSuccess) return e;
       configured[dev] = true;
     }
@@ -1103,7 +1242,7 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
     attr[1].val.clusterDim.z = 1;
     cfg.numAttrs = 2;
   }
-  return cudaLaunchKernelEx(&cfg, kern, wmap, xmap, p);
+  return cudaLaunchKernelEx(&cfg, kern, wmap, xmap, ymap != nullptr ? *ymap : xmap, p);
 }
 
 #ifdef ULLM_CUDA_TUNING
@@ -1250,6 +1389,16 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   p.wait_ns = (uint64_t)(a.wait_limit_ms != 0 ? a.wait_limit_ms : kDefaultWaitLimitMs) * 1000000ull;
   p.residual = pair ? nullptr : a.residual;
   p.res_stride = a.res_stride;
+#ifdef ULLM_CUDA_TUNING
+  p.stats = nullptr;
+  p.dbg = (uint32_t)env_int("ULLM_CUDA_GEMM_DBG");
+  static const bool want_stats = env_int("ULLM_CUDA_GEMM_STATS") == 1;
+  if (want_stats) {
+    static unsigned long long *buf = nullptr;
+    if (buf == nullptr && cudaMalloc(reinterpret_cast<void **>(&buf), 9 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
+    if (buf != nullptr && cudaMemsetAsync(buf, 0, 9 * sizeof(unsigned long long), stream) == cudaSuccess) p.stats = buf;
+  }
+#endif
   if (pair) {  // gate|up to scratch as bf16, combined afterwards
     p.y = scratch + pl.off_pair;
     p.y_stride = a.n;
@@ -1260,39 +1409,64 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
     p.y_dtype = a.y_dtype;
   }
   CUtensorMap wmap, xmap;
-  static const bool whole_k_stage = env_int("ULLM_CUDA_GEMM_STAGE_K") == 128;
-  const uint32_t ks = (a.encoding == FP8 && pl.tt == 256 && (pl.cta_pairs || !whole_k_stage)) ? 64u : 128u;
+  // k per stage of the widest FP8 tiles: CTA pairs hold half the tokens each, so four whole k-blocks fit and every
+  // barrier round trip covers twice the work (measured 1.12 vs 0.98 PFLOP/s at 2048 x 14336 x 4096); a single CTA's
+  // 256-token stages are too large for more than two whole k-blocks, it takes half k-blocks
+  static const int forced_stage_k = env_int("ULLM_CUDA_GEMM_STAGE_K");
+  uint32_t ks = 128u;
+  if (a.encoding == FP8 && pl.tt == 256) {
+    ks = pl.cta_pairs ? 128u : 64u;
+    if (forced_stage_k == 64 || forced_stage_k == 128) ks = (uint32_t)forced_stage_k;
+  }
+  // bf16 results of wide FP8 tiles leave by TMA stores when the output allows it (16-byte aligned rows)
+  CUtensorMap ymap_store;
+  const CUtensorMap *ymap = nullptr;
+  if (a.encoding == FP8 && pl.tt >= 128 && p.y_dtype == ULLM_CUDA_DTYPE_BF16 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 &&
+      (p.y_stride * 2) % 16 == 0 && make_y_map(&ymap_store, p.y, a.m, a.n, p.y_stride))
+    ymap = &ymap_store;
   // a CTA of a pair loads half of the tile's tokens
   if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding, ks) ||
       !make_x_map(&xmap, planes, a.m, a.k, (uint32_t)(pl.cta_pairs ? pl.tt / 2 : pl.tt), ks))
     return cudaErrorInvalidValue;
   if (a.encoding == AQ4) {
     switch (pl.tt) {
-      case 16: e = launch_tile<AQ4, 16, 1>(stream, wmap, xmap, p, pl.grid); break;
-      case 32: e = launch_tile<AQ4, 32, 1>(stream, wmap, xmap, p, pl.grid); break;
-      case 64: e = launch_tile<AQ4, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
-      default: e = launch_tile<AQ4, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 16: e = launch_tile<AQ4, 16, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      case 32: e = launch_tile<AQ4, 32, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      case 64: e = launch_tile<AQ4, 64, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      default: e = launch_tile<AQ4, 128, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
     }
   } else {
     switch (pl.tt) {
-      case 16: e = launch_tile<FP8, 16, 1>(stream, wmap, xmap, p, pl.grid); break;
-      case 32: e = launch_tile<FP8, 32, 1>(stream, wmap, xmap, p, pl.grid); break;
-      case 64: e = launch_tile<FP8, 64, 1>(stream, wmap, xmap, p, pl.grid); break;
-      case 128: e = launch_tile<FP8, 128, 1>(stream, wmap, xmap, p, pl.grid); break;
+      case 16: e = launch_tile<FP8, 16, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      case 32: e = launch_tile<FP8, 32, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      case 64: e = launch_tile<FP8, 64, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
+      case 128: e = launch_tile<FP8, 128, 1>(stream, wmap, xmap, ymap, p, pl.grid); break;
       default:
         if (pl.cta_pairs)
-          e = launch_tile<FP8, 256, 1, 64, true>(stream, wmap, xmap, p, pl.grid);
+          e = ks == 64 ? launch_tile<FP8, 256, 1, 64, true>(stream, wmap, xmap, ymap, p, pl.grid)
+                       : launch_tile<FP8, 256, 1, BKB, true>(stream, wmap, xmap, ymap, p, pl.grid);
         else if (ks == 64)
-          e = pl.rt == 2 ? launch_tile<FP8, 256, 2, 64>(stream, wmap, xmap, p, pl.grid)
-                         : launch_tile<FP8, 256, 1, 64>(stream, wmap, xmap, p, pl.grid);
+          e = pl.rt == 2 ? launch_tile<FP8, 256, 2, 64>(stream, wmap, xmap, ymap, p, pl.grid)
+                         : launch_tile<FP8, 256, 1, 64>(stream, wmap, xmap, ymap, p, pl.grid);
         else
-          e = pl.rt == 2 ? launch_tile<FP8, 256, 2>(stream, wmap, xmap, p, pl.grid)
-                         : launch_tile<FP8, 256, 1>(stream, wmap, xmap, p, pl.grid);
+          e = pl.rt == 2 ? launch_tile<FP8, 256, 2>(stream, wmap, xmap, ymap, p, pl.grid)
+                         : launch_tile<FP8, 256, 1>(stream, wmap, xmap, ymap, p, pl.grid);
         break;
     }
   }
   if (e != cudaSuccess) return e;
   ++*launches;
+#ifdef ULLM_CUDA_TUNING
+  if (p.stats != nullptr) {  // ULLM_CUDA_GEMM_STATS=1: share of the time each single-thread role spent waiting
+    unsigned long long h[9];
+    if (cudaStreamSynchronize(stream) == cudaSuccess && cudaMemcpy(h, p.stats, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess) {
+      auto pct = [](unsigned long long a, unsigned long long b) { return b ? 100.0 * (double)a / (double)b : 0.0; };
+      std::fprintf(stderr, "gemm stats m=%u n=%u k=%u pairs=%d tt=%d rt=%d: TMA waits empty %.1f%% | MMA waits full %.1f%% acc_empty %.1f%% | epilogue waits acc_full %.1f%% (clocks/CTA %.0f)\n",
+                   a.m, a.n, a.k, (int)pl.cta_pairs, pl.tt, pl.rt, pct(h[1], h[0]), pct(h[4], h[3]), pct(h[5], h[3]), pct(h[7], h[6]),
+                   (double)h[6] / (double)pl.grid);
+    }
+  }
+#endif
   if (pair) {
     dim3 g2((a.n / 2 + 255) / 256 > 64 ? 64 : (a.n / 2 + 255) / 256, a.m);
     swiglu_kernel<<<g2, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(scratch + pl.off_pair), a.n / 2,
