@@ -1312,10 +1312,13 @@ Plan make_plan(const Context *ctx, const LinearArgs &a, bool allow_partials) {
   uint32_t grid = pl.tiles < workers ? pl.tiles : workers;
   // Whole tiles only: ceil(tiles / grid) rounds.  Hybrid: the full rounds whole, the remaining tiles cut
   // along K over the workers, which costs each CTA up to two partial tiles (written, fenced, read back).
-  // Costs in k-block times; a partial of 128 x 256 fp32 is worth about five of them.
+  // Costs in k-block times.
   static const int forced_whole = env_int("ULLM_CUDA_GEMM_WHOLE");
   const uint32_t full = pl.tiles / workers, rem = pl.tiles % workers;
-  const double part = 5.0 * pl.rt * pl.tt / 256.0;
+  // Measured on B200 (whole tiles against hybrid over 15 shapes per encoding): a kernel with partial tiles pays
+  // about 40 us at 256 tokens per tile, 10 us at 128, a few us below, whatever the matrix size.
+  double part = (pl.tt >= 256 ? 24.0 : pl.tt >= 128 ? 12.0 : 8.0) * pl.rt;
+  if (a.encoding == AQ4) part /= 2.5;  // its k-blocks take 2.5 times as long
   const double cost_whole = (double)((pl.tiles + workers - 1) / workers) * kb;
   const double cost_hybrid = (double)full * kb + (rem ? (double)rem * kb / workers + 2.0 * part : 0.0);
   const bool hybrid = allow_partials && rem != 0 && (uint64_t)rem * kb >= 8 && forced_whole != 1 &&
