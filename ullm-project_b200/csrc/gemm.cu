@@ -776,6 +776,38 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       };
+      // bf16 results (whole tiles): this warp's 32 rows x 32 tokens go to its own shared-memory slot and leave by one
+      // TMA store (clipped at the matrix edges), so the stores cost the warp 32 shared-memory writes
+      auto stage_out = [&](int r, uint32_t c, const float (&v)[CH]) {
+        if constexpr (CH == 32) {
+          const uint32_t slot_addr = out0 + ((e * p.out_bufs + (out_n % p.out_bufs)) << 11);
+          const uint32_t row = n0 + r * BM + row_in_tile;
+          if (lane == 0) {
+            if (p.out_bufs > 1u)
+              bulk_wait_read<1>();
+            else
+              bulk_wait_read<0>();
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < CH; ++i) {
+            const uint32_t tok = m0 + c + i;
+            float o = v[i] * (mult * __ldg(p.tok_scale + (tok < p.m ? tok : 0u)));
+            if (p.residual != nullptr && tok < p.m && row < p.n) o += p.residual[(uint64_t)tok * p.res_stride + row];
+            const __nv_bfloat16 h = __float2bfloat16_rn(o);
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(slot_addr + (uint32_t)i * 64u + lane * 2u),
+                         "h"(*reinterpret_cast<const unsigned short *>(&h))
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_y, slot_addr, (int)(n0 + r * BM + quarter * 32u), (int)(m0 + c));
+            bulk_commit();
+          }
+          ++out_n;
+        }
+      };
       if (ENC == FP8) {
         const uint32_t buf = seg % NB, use = seg / NB;
         GEMM_STAT_WAIT(st_wait_a, ok = ok && mbar_wait(acc_full(buf), use & 1u, wctl));
@@ -801,37 +833,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
                   f[i] = (NCAT ? fmaf(__uint_as_float(v2[i]), 0.0625f, __uint_as_float(v[i])) : __uint_as_float(v[i])) * sc;
-                if (CH == 32 && p.out_bufs != 0u && direct) {
-                  // bf16 results: this warp's 32 rows x 32 tokens go to its own shared-memory slot and leave by one
-                  // TMA store (clipped at the matrix edges), so the stores cost the warp 32 shared-memory writes
-                  const uint32_t slot_addr = out0 + ((e * p.out_bufs + (out_n % p.out_bufs)) << 11);
-                  if (lane == 0) {
-                    if (p.out_bufs > 1u)
-                      bulk_wait_read<1>();
-                    else
-                      bulk_wait_read<0>();
-                  }
-                  __syncwarp();
-#pragma unroll
-                  for (int i = 0; i < CH; ++i) {
-                    const uint32_t tok = m0 + col0 + c + i;
-                    float o = f[i] * (mult * __ldg(p.tok_scale + (tok < p.m ? tok : 0u)));
-                    if (p.residual != nullptr && tok < p.m && row < p.n) o += p.residual[(uint64_t)tok * p.res_stride + row];
-                    const __nv_bfloat16 h = __float2bfloat16_rn(o);
-                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(slot_addr + (uint32_t)i * 64u + lane * 2u),
-                                 "h"(*reinterpret_cast<const unsigned short *>(&h))
-                                 : "memory");
-                  }
-                  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                  __syncwarp();
-                  if (lane == 0) {
-                    tma_store_2d(&tmap_y, slot_addr, (int)(n0 + r * BM + quarter * 32u), (int)(m0 + col0 + c));
-                    bulk_commit();
-                  }
-                  ++out_n;
-                } else {
+                if (CH == 32 && p.out_bufs != 0u && direct)
+                  stage_out(r, col0 + c, f);
+                else
                   emit(r, col0 + c, f, direct);
-                }
               }
             }
           }
@@ -926,7 +931,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             float f[CH];
 #pragma unroll
             for (int i = 0; i < CH; ++i) f[i] = acc[c + i];
-            emit(0, col0 + c, f, direct);
+            if (CH == 32 && p.out_bufs != 0u && direct)
+              stage_out(0, col0 + c, f);
+            else
+              emit(0, col0 + c, f, direct);
           }
         }
       }
@@ -1178,10 +1186,13 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
   size_t ns = 0, rs = 0;
+  constexpr size_t out_one = (size_t)kEpiWarps * 2048;  // one staging slot per epilogue warp
   if (ENC == AQ4) {
-    ns = (budget - 3 * raw_stage) / stage;
+    // the epilogue's staging slots come out of the nibble ring's share
+    const size_t out_aq4 = (TT >= 128 && ymap != nullptr) ? out_one : 0;
+    ns = (budget - out_aq4 - 3 * raw_stage) / stage;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
-    rs = (budget - ns * stage) / raw_stage;
+    rs = (budget - out_aq4 - ns * stage) / raw_stage;
     if (rs > MAX_RAW) rs = MAX_RAW;
   } else {
     ns = budget / stage;
@@ -1191,8 +1202,12 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   // if they fit beside the stages, else one; a stage is given up only if not even that fits
   size_t out_bytes = 0;
   p.out_bufs = 0;
+  if (ENC == AQ4 && TT >= 128 && ymap != nullptr) {
+    p.out_bufs = 1;
+    out_bytes = out_one;
+  }
   if (ENC == FP8 && TT >= 128 && ymap != nullptr) {
-    constexpr size_t one = (size_t)kEpiWarps * 2048;
+    constexpr size_t one = out_one;
     if (ns * stage + 2 * one <= budget) {
       p.out_bufs = 2;
     } else if (ns * stage + one <= budget) {
@@ -1424,7 +1439,7 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   // bf16 results of wide FP8 tiles leave by TMA stores when the output allows it (16-byte aligned rows)
   CUtensorMap ymap_store;
   const CUtensorMap *ymap = nullptr;
-  if (a.encoding == FP8 && pl.tt >= 128 && p.y_dtype == ULLM_CUDA_DTYPE_BF16 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 &&
+  if (pl.tt >= 128 && p.y_dtype == ULLM_CUDA_DTYPE_BF16 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 &&
       (p.y_stride * 2) % 16 == 0 && make_y_map(&ymap_store, p.y, a.m, a.n, p.y_stride))
     ymap = &ymap_store;
   // a CTA of a pair loads half of the tile's tokens
