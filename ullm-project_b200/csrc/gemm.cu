@@ -94,12 +94,13 @@ struct GemmParams {
   unsigned long long *stats;  // tuning builds: clocks the single-thread roles spent waiting, summed over CTAs
   uint32_t dbg;               // timing experiments (results are wrong): 1 = rest plane read as e4m3, 2 = rest plane skipped,
                               // 4 = activation planes not loaded, 8 = no MMA issued, 16 = weights not loaded,
-                              // 32 = nothing stored, 64 = accumulators not read, 128 = plain arrive instead of commit
+                              // 32 = nothing stored, 64 = accumulators not read, 128 = plain arrive instead of commit,
+                              // 256 = AQ4 converters only pass their barriers, 512 = AQ4 epilogue skips the per-group drain
 #endif
 };
 
 #ifdef ULLM_CUDA_TUNING
-#define GEMM_STAT_DECL unsigned long long st_wait_a = 0, st_wait_b = 0; const long long st_t0 = clock64();
+#define GEMM_STAT_DECL unsigned long long st_wait_a = 0, st_wait_b = 0, st_wait_c = 0; const long long st_t0 = clock64();
 #define GEMM_STAT_WAIT(var, expr) do { const long long t_ = clock64(); expr; var += (unsigned long long)(clock64() - t_); } while (0)
 #define GEMM_STAT_FLUSH(base) do { if (p.stats != nullptr) { atomicAdd(p.stats + (base), (unsigned long long)(clock64() - st_t0)); \
   atomicAdd(p.stats + (base) + 1, st_wait_a); atomicAdd(p.stats + (base) + 2, st_wait_b); } } while (0)
@@ -123,7 +124,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef ULLM_GEMM_TEST_WAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -553,6 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t slot = 0, round = 0, seg = 0, batch = 0, in_batch = 0;
       bool ok = true;
 #ifdef ULLM_CUDA_TUNING
+      unsigned long long sq_fence = 0, sq_issue = 0, sq_commit = 0;
       const uint32_t id_lo = (p.dbg & 1u) ? idesc : idesc_lo;
       const bool skip_lo = (p.dbg & 2u) != 0u, skip_mma = (p.dbg & 8u) != 0u;
 #else
@@ -573,12 +579,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             buf = batch % NB;
             const uint32_t use = batch / NB;
             fresh = 1u;
-            if (in_batch == 0 && use >= 1) ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl);
-            ok = ok && mbar_wait(a_full(slot), round & 1u, wctl);
+            if (in_batch == 0 && use >= 1) GEMM_STAT_WAIT(st_wait_b, ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl));
+            GEMM_STAT_WAIT(st_wait_c, ok = ok && mbar_wait(a_full(slot), round & 1u, wctl));
           }
           GEMM_STAT_WAIT(st_wait_a, ok = ok && mbar_wait(full(slot), round & 1u, wctl));
           if (!ok) break;
+#ifdef ULLM_CUDA_TUNING
+          const long long tq0 = clock64();
+#endif
           tc_fence_after();
+#ifdef ULLM_CUDA_TUNING
+          const long long tq1 = clock64();
+#endif
           const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
@@ -597,6 +609,9 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
           }
+#ifdef ULLM_CUDA_TUNING
+          const long long tq2 = clock64();
+#endif
           // the stage may be refilled when these MMAs are done (in both CTAs of a pair)
 #ifdef ULLM_CUDA_TUNING
           if ((p.dbg & 128u) != 0u && !PAIR) {
@@ -623,6 +638,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               tc_commit(acc_full(buf));
             }
           }
+#ifdef ULLM_CUDA_TUNING
+          const long long tq3 = clock64();
+          sq_fence += (unsigned long long)(tq1 - tq0);
+          sq_issue += (unsigned long long)(tq2 - tq1);
+          sq_commit += (unsigned long long)(tq3 - tq2);
+#endif
           if (++slot == NS) {
             slot = 0;
             ++round;
@@ -630,7 +651,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ++seg;
       }
+#ifdef ULLM_CUDA_TUNING
+      if (p.stats != nullptr) {
+        atomicAdd(p.stats + 13, sq_fence);
+        atomicAdd(p.stats + 14, sq_issue);
+        atomicAdd(p.stats + 15, sq_commit);
+      }
+#endif
       GEMM_STAT_FLUSH(3);
+#ifdef ULLM_CUDA_TUNING
+      if (p.stats != nullptr) atomicAdd(p.stats + 12, st_wait_c);
+#endif
     }
   } else if (warp == 2) {
     // ---- AQ4: TMA of the packed nibble tiles (weights: nothing to wait for) ------------------
@@ -667,9 +698,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t ct = threadIdx.x - kConvWarp0 * 32;
       uint32_t slot = 0, round = 0, rslot = 0, rround = 0;
       bool ok = true;
+      GEMM_STAT_DECL
       while (ok && walk.next(&sg)) {
         for (uint32_t i = 0; i < sg.nkb; ++i) {
-          if (!mbar_wait(raw_full(rslot), rround & 1u, wctl)) {
+          bool got = true;
+          GEMM_STAT_WAIT(st_wait_a, got = mbar_wait(raw_full(rslot), rround & 1u, wctl));
+          if (!got) {
             ok = false;
             break;
           }
@@ -685,10 +719,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                            : "r"(addr));
             }
           }
-          if (round > 0 && !mbar_wait(empty(slot), (round - 1) & 1u, wctl)) {
+          if (round > 0) GEMM_STAT_WAIT(st_wait_b, got = mbar_wait(empty(slot), (round - 1) & 1u, wctl));
+          if (!got) {
             ok = false;
             break;
           }
+#ifdef ULLM_CUDA_TUNING
+          if ((p.dbg & 256u) == 0u)
+#endif
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
             const uint32_t a_addr = smem0 + slot * STAGE_BYTES + r * A_BYTES;
@@ -727,6 +765,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+#ifdef ULLM_CUDA_TUNING
+      if (ct == 0) GEMM_STAT_FLUSH(9);
+#endif
     }
   } else if (warp >= kEpiWarp0) {
     // ---- epilogue: warp e covers TMEM lanes 32*(warp % 4) .. +31 and half of the token columns ----
@@ -865,10 +906,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t buf = batch % NB, use = batch / NB;
             const float sc = sc_next;
             if (g + 1 < sg.nkb && row < p.n) sc_next = __half2float(srow[g + 1]);
-            ok = mbar_wait(acc_full(buf), use & 1u, wctl);
+            GEMM_STAT_WAIT(st_wait_a, ok = mbar_wait(acc_full(buf), use & 1u, wctl));
             if (!ok) break;
             tc_fence_after();
+#ifdef ULLM_CUDA_TUNING
+            if (active && (p.dbg & 512u) == 0u) {
+#else
             if (active) {
+#endif
 #pragma unroll
               for (int c = 0; c < COLS; c += CH) {
                 uint32_t v[CH], v2[CH];
@@ -1413,8 +1458,8 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   static const bool want_stats = env_int("ULLM_CUDA_GEMM_STATS") == 1;
   if (want_stats) {
     static unsigned long long *buf = nullptr;
-    if (buf == nullptr && cudaMalloc(reinterpret_cast<void **>(&buf), 9 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
-    if (buf != nullptr && cudaMemsetAsync(buf, 0, 9 * sizeof(unsigned long long), stream) == cudaSuccess) p.stats = buf;
+    if (buf == nullptr && cudaMalloc(reinterpret_cast<void **>(&buf), 16 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
+    if (buf != nullptr && cudaMemsetAsync(buf, 0, 16 * sizeof(unsigned long long), stream) == cudaSuccess) p.stats = buf;
   }
 #endif
   if (pair) {  // gate|up to scratch as bf16, combined afterwards
@@ -1476,12 +1521,17 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   ++*launches;
 #ifdef ULLM_CUDA_TUNING
   if (p.stats != nullptr) {  // ULLM_CUDA_GEMM_STATS=1: share of the time each single-thread role spent waiting
-    unsigned long long h[9];
+    unsigned long long h[16];
     if (cudaStreamSynchronize(stream) == cudaSuccess && cudaMemcpy(h, p.stats, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess) {
       auto pct = [](unsigned long long a, unsigned long long b) { return b ? 100.0 * (double)a / (double)b : 0.0; };
       std::fprintf(stderr, "gemm stats m=%u n=%u k=%u pairs=%d tt=%d rt=%d: TMA waits empty %.1f%% | MMA waits full %.1f%% acc_empty %.1f%% | epilogue waits acc_full %.1f%% (clocks/CTA %.0f)\n",
                    a.m, a.n, a.k, (int)pl.cta_pairs, pl.tt, pl.rt, pct(h[1], h[0]), pct(h[4], h[3]), pct(h[5], h[3]), pct(h[7], h[6]),
                    (double)h[6] / (double)pl.grid);
+      std::fprintf(stderr, "  MMA thread: fence %.1f%% issue %.1f%% commits %.1f%% of its %.0f clocks\n", pct(h[13], h[3]), pct(h[14], h[3]),
+                   pct(h[15], h[3]), (double)h[3] / (double)(pl.cta_pairs ? pl.grid / 2 : pl.grid));
+      if (a.encoding == AQ4)
+        std::fprintf(stderr, "  AQ4: MMA waits converted tile %.1f%% | converter waits nibbles %.1f%% free tile %.1f%% (clocks/CTA %.0f)\n",
+                     pct(h[12], h[3]), pct(h[10], h[9]), pct(h[11], h[9]), (double)h[9] / (double)pl.grid);
     }
   }
 #endif
