@@ -91,6 +91,37 @@ def test_gemm_swiglu_epilogue_and_strides(gpu, encoding):
     dw.close()
 
 
+@pytest.mark.parametrize("encoding", ENCODINGS)
+@pytest.mark.parametrize("m,n,k", [(300, 392, 512), (600, 1024, 384), (129, 136, 256)])
+def test_wide_tiles_every_way_out(gpu, encoding, m, n, k):
+    """More than 128 tokens: FP8 tiles are shared by a pair of CTAs (256 weight rows, the second CTA's rows partly
+    or wholly past the matrix edge) and bf16 results leave through shared memory and TMA stores, clipped at both
+    edges.  Output rows that are not 16-byte aligned, fp32 output and partial tiles take the per-element stores.
+    All of them must give the same answer, with and without a residual."""
+    ctx, q = gpu
+    w = o.synth_weights(SEED, 2800 + n, n, k)
+    x = o.synth_activations(SEED, 2801 + m, m, k)
+    res = o.synth_normal(SEED, 2802, 0, m * n).reshape(m, n).astype(np.float32)
+    dw = DeviceWeight(ctx, q, w, encoding)
+    wdq = oracle_dequantize(*oracle_quantize(w, encoding), encoding)
+    ref = oracle_linear(x, wdq)
+    ref_res = oracle_linear(x, wdq, residual=res)
+    y, r = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM)
+    assert r.device_flags == 0
+    check(y, ref, (encoding, m, n, k, "contiguous"))
+    for stride in (n + 8, n + 3):  # 16-byte aligned rows (bulk stores), odd rows (per-element stores)
+        ys, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, y_stride=stride)
+        assert np.array_equal(ys.view(np.uint32), y.view(np.uint32)), (encoding, stride)
+    yr, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, residual=res)
+    check(yr, ref_res, (encoding, m, n, k, "residual"))
+    yr2, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, residual=res, y_stride=n + 3)
+    assert np.array_equal(yr2.view(np.uint32), yr.view(np.uint32))
+    yf, _ = run_linear(ctx, q, dw, x, kernel=U.KERNEL_GEMM, y_dtype=U.DTYPE_F32)
+    assert np.array_equal(o.bf16_round(yf).view(np.uint32), y.view(np.uint32))
+    assert dw.canaries_intact(q)
+    dw.close()
+
+
 def test_auto_selects_the_faster_kernel_for_the_token_count(gpu):
     """AUTO: the matvec for one token (AQ4: up to four), the tensor-core GEMM above that where it serves the shape."""
     ctx, q = gpu
