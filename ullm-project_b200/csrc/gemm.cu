@@ -42,6 +42,14 @@
 // Accumulators are double-buffered in tensor memory, so the epilogue of one tile overlaps the MMAs of
 // the next.  A tile whose k-blocks fall into several CTAs' shares is finished by the CTA that arrives
 // last at the tile's counter, adding the fp32 partials in a fixed order (deterministic).
+// Wide FP8 tiles (more than 128 tokens) run on PAIRS of CTAs (clusters of two, tcgen05 cta_group::2): 256
+// weight rows x 256 tokens per pair, each CTA loading its own weight rows and half of the token rows, one
+// thread of the pair issuing the MMAs for both SMs; see the comment above the kernel.  bf16 results of tiles
+// of 128 tokens or more leave through shared memory and TMA stores, one 32 x 32 piece per epilogue warp.
+// Measured on B200 (tuning build, operations switched off one at a time): a barrier round trip between
+// the single-thread roles costs about 0.2 us per stage and does not overlap the MMAs of that stage, and
+// per-element result stores cost 42 us of a 243 us kernel; hence whole-k-block stages where they fit
+// (pairs), bulk stores, and whole tiles instead of a k-split tail for wide tiles.
 // Every mbarrier wait is bounded in time; on expiry the kernel flags the context and unwinds
 // (tensor memory is always released).
 #include "internal.hpp"
