@@ -546,8 +546,8 @@ typedef struct ullm_cuda_stack_desc_t {
 #define ULLM_CUDA_STACK_FLAG_KEEP_ACTIVATIONS UINT32_C(2) /* one activation set per layer, readable after a step */
 #define ULLM_CUDA_STACK_FLAG_NCCL_ONLY UINT32_C(4) /* sum over ranks with ncclAllReduce even for decode steps */
 /* How the kernel that follows a row-parallel linear gathers the ranks' partial sums (fused all-reduce, decode):
- * by default every thread block reads all ranks' slots up to 2 ranks, and from 4 ranks on the blocks of a
- * thread-block cluster share one reading through distributed shared memory.  These two flags force one way. */
+ * by default the blocks of a thread-block cluster share one reading of the ranks' slots through distributed shared
+ * memory; the alternative is that every thread block reads all ranks' slots itself.  These two flags force one way. */
 #define ULLM_CUDA_STACK_FLAG_GATHER_PER_BLOCK UINT32_C(8)
 #define ULLM_CUDA_STACK_FLAG_GATHER_PER_CLUSTER UINT32_C(16)
 
