@@ -389,6 +389,13 @@ __device__ __forceinline__ uint32_t nibble_bytes_to_e4m3(uint32_t b) {
   return r0 + m * 129u;                             // negative: + 1 -> 8 - u, and bit 7
 }
 
+// k-blocks per pipeline stage.  A barrier round trip between the TMA thread and the MMA thread costs about as much as
+// the MMAs of a narrow k-block, so the narrow FP8 tiles of batched decode move two k-blocks per stage.
+template <uint32_t ENC, int TT, int KS, bool PAIR>
+__host__ __device__ constexpr uint32_t kps_of() {
+  return (ENC == FP8 && !PAIR && KS == BKB && TT <= 64) ? 2u : 1u;
+}
+
 // PAIR: the kernel is launched in clusters of two CTAs that share every tile: 256 weight rows (128 per CTA) x TT
 // tokens, each CTA loading its own weight rows and HALF of the token rows; rank 0 issues tcgen05.mma.cta_group::2
 // for both, so each SM's tensor core reads half of the activation tile from its own shared memory and the other
@@ -407,7 +414,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t A_STAGE = (uint32_t)BM * KS;       // one row block of the stage
   constexpr uint32_t B_TOK = PAIR ? TT / 2 : TT;        // token rows this CTA loads
   constexpr uint32_t B_BYTES = B_TOK * KS;              // one activation plane of the stage
-  constexpr uint32_t STAGE_BYTES = RT * A_STAGE + 2 * B_BYTES;
+  constexpr uint32_t KPS = kps_of<ENC, TT, KS, PAIR>();  // k-blocks per stage
+  constexpr uint32_t SUB_BYTES = RT * A_STAGE + 2 * B_BYTES;  // operands of one k-block (or half of one)
+  constexpr uint32_t STAGE_BYTES = KPS * SUB_BYTES;
   // Up to 64 tokens the two activation planes, adjacent in shared memory, are ONE operand of 2*TT rows: a
   // single MMA per k-slice leaves A.hi in columns [0,TT) and A.lo in [TT,2TT) and the epilogue adds them.
   // A narrow MMA costs the tensor pipe about as much as a wide one, so this halves the pipe time where
@@ -506,7 +515,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       while (ok && walk.next(&sg)) {
         uint32_t n0, m0;
         tile_origin(sg.tile, &n0, &m0);
-        for (uint32_t i = 0; i < sg.nkb * SUBS; ++i) {
+        for (uint32_t i = 0; i < sg.nkb * SUBS; i += KPS) {
+          const uint32_t cnt = sg.nkb * SUBS - i < KPS ? sg.nkb * SUBS - i : KPS;  // k-blocks in this stage
           bool got = true;
           if (round > 0) GEMM_STAT_WAIT(st_wait_a, got = mbar_wait(empty(slot), (round - 1) & 1u, wctl));
           if (!got) {
@@ -536,14 +546,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 #else
             constexpr bool no_x = false, no_w = false;
 #endif
-            mbar_expect_tx(full(slot), ((ENC == FP8 && !no_w) ? RT * A_STAGE : 0u) + (no_x ? 0u : 2 * B_BYTES));
-            if (ENC == FP8 && !no_w) {
+            mbar_expect_tx(full(slot), cnt * (((ENC == FP8 && !no_w) ? RT * A_STAGE : 0u) + (no_x ? 0u : 2 * B_BYTES)));
+            for (uint32_t j = 0; j < cnt; ++j) {
+              const uint32_t sa = a_addr + j * SUB_BYTES;
+              const int kj = kx + (int)(j * KS);
+              if (ENC == FP8 && !no_w) {
 #pragma unroll
-              for (int r = 0; r < RT; ++r) tma_load_2d(a_addr + r * A_STAGE, &tmap_w, kx, (int)(n0 + r * BM), full(slot));
-            }
-            if (!no_x) {
-              tma_load_3d(a_addr + RT * A_STAGE, &tmap_x, kx, (int)m0, 0, full(slot));
-              tma_load_3d(a_addr + RT * A_STAGE + B_BYTES, &tmap_x, kx, (int)m0, 1, full(slot));
+                for (int r = 0; r < RT; ++r) tma_load_2d(sa + r * A_STAGE, &tmap_w, kj, (int)(n0 + r * BM), full(slot));
+              }
+              if (!no_x) {
+                tma_load_3d(sa + RT * A_STAGE, &tmap_x, kj, (int)m0, 0, full(slot));
+                tma_load_3d(sa + RT * A_STAGE + B_BYTES, &tmap_x, kj, (int)m0, 1, full(slot));
+              }
             }
           }
           if (++slot == NS) {
@@ -577,7 +591,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t use = seg / NB;
           if (use >= 1) GEMM_STAT_WAIT(st_wait_b, ok = mbar_wait(acc_empty(buf), (use - 1) & 1u, wctl));
         }
-        for (uint32_t i = 0; i < sg.nkb * SUBS && ok; ++i) {
+        for (uint32_t i = 0; i < sg.nkb * SUBS && ok; i += KPS) {
+          const uint32_t cnt = sg.nkb * SUBS - i < KPS ? sg.nkb * SUBS - i : KPS;  // k-blocks in this stage
           uint32_t fresh = i == 0 ? 1u : 0u;
           if (ENC == AQ4) {
             buf = batch % NB;
@@ -595,21 +610,25 @@ __global__ void __launch_bounds__(kThreads, 1)
 #ifdef ULLM_CUDA_TUNING
           const long long tq1 = clock64();
 #endif
-          const uint32_t a_addr = smem0 + slot * STAGE_BYTES, hi_addr = a_addr + RT * A_STAGE, lo_addr = hi_addr + B_BYTES;
+          for (uint32_t j = 0; j < cnt; ++j) {
+            const uint32_t a_addr = smem0 + slot * STAGE_BYTES + j * SUB_BYTES, hi_addr = a_addr + RT * A_STAGE,
+                           lo_addr = hi_addr + B_BYTES;
 #pragma unroll
-          for (int r = 0; r < RT; ++r) {
-            const uint32_t d = tmem_base + buf * BUF_COLS + in_batch * ACC_COLS + r * MMA_N;
+            for (int r = 0; r < RT; ++r) {
+              const uint32_t d = tmem_base + buf * BUF_COLS + in_batch * ACC_COLS + r * MMA_N;
 #pragma unroll
-            for (int k4 = 0; k4 < KS / 32; ++k4) {
-              // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
-              const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
-              if (skip_mma) continue;
-              if (PAIR) {
-                tc_mma_pair(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-                if (!skip_lo) tc_mma_pair(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
-              } else {
-                tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, (fresh && k4 == 0) ? 0u : 1u);
-                if (!NCAT && !skip_lo) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
+              for (int k4 = 0; k4 < KS / 32; ++k4) {
+                // 32 e4m3 along K = 32 bytes inside the swizzled row: advance the start address only
+                const uint64_t adesc = smem_desc<KS>(a_addr + r * A_STAGE + k4 * 32);
+                const uint32_t acc = (fresh && j == 0 && k4 == 0) ? 0u : 1u;
+                if (skip_mma) continue;
+                if (PAIR) {
+                  tc_mma_pair(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, acc);
+                  if (!skip_lo) tc_mma_pair(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
+                } else {
+                  tc_mma_e4m3(d, adesc, smem_desc<KS>(hi_addr + k4 * 32), idesc, acc);
+                  if (!NCAT && !skip_lo) tc_mma_e4m3(d, adesc, smem_desc<KS>(lo_addr + k4 * 32), id_lo, 1u);
+                }
               }
             }
           }
@@ -634,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               ++batch;
               in_batch = 0;
             }
-          } else if (i + 1 == sg.nkb * SUBS) {
+          } else if (i + cnt == sg.nkb * SUBS) {
             if (PAIR) {
               tc_commit_pair(acc_full(buf));
               tc_commit_pair(map_to_cta(acc_full(buf), 1u));
@@ -1231,7 +1250,7 @@ bool make_y_map(CUtensorMap *map, const void *y, uint32_t m, uint32_t n, uint64_
 template <uint32_t ENC, int TT, int RT, int KS = BKB, bool PAIR = false>
 cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUtensorMap &xmap, const CUtensorMap *ymap,
                         GemmParams p, uint32_t grid) {
-  constexpr size_t stage = (size_t)RT * BM * KS + 2 * (size_t)(PAIR ? TT / 2 : TT) * KS;
+  constexpr size_t stage = kps_of<ENC, TT, KS, PAIR>() * ((size_t)RT * BM * KS + 2 * (size_t)(PAIR ? TT / 2 : TT) * KS);
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
   size_t ns = 0, rs = 0;
