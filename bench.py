@@ -102,7 +102,7 @@ class ClockSampler:
 # DRAM traffic of the step's dominant kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum per launch),
 # captured on single-kernel workloads of full shape and scaled to the step by algorithmic bytes: the kernels read
 # each weight byte once, so traffic / algorithmic bytes is the same ratio for every matvec of the step.
-TRAFFIC_RATIO = {"fp8": 1.000, "aq4": 1.000}
+TRAFFIC_RATIO = {"fp8": 1.007, "aq4": 1.004}  # profiles/matvec_fp8_m1_n57344_k8192.md, matvec_aq4_m1_n28672_k4096.md
 TRAFFIC_NOTE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of the matvec kernel on its full-shape single-kernel "
                 "workload (profiles/matvec_*.md), scaled to one step by algorithmic bytes")
 
