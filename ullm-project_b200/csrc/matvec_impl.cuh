@@ -588,7 +588,10 @@ __global__ void __launch_bounds__(T, 1) matvec_kernel(const Params p) {
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t warp = threadIdx.x >> 5;
   // a warp set (S consecutive warps) works on one row group at a time
-  const uint32_t gwarp = (blockIdx.x * (T / 32) + warp) / S;
+  // set w of block b takes row groups w * gridDim.x + b, + nwarps, ...: with fewer groups than warp sets every SM
+  // still streams its share (8192 rows in two-row groups fill 27 or 28 of the 32 warps of all 148 blocks, not all 32
+  // warps of 128 blocks)
+  const uint32_t gwarp = (warp / S) * gridDim.x + blockIdx.x;
   const uint32_t nwarps = gridDim.x * (T / 32) / S;
   const uint32_t slice = S > 1 ? warp % S : 0u;
   const bool pair = p.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
@@ -984,8 +987,8 @@ cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p_
   const uint32_t groups = pair ? (p.n / 2 + R / 2 - 1) / (R / 2 > 0 ? R / 2 : 1) : (p.n + R - 1) / R;
   uint32_t grid = (uint32_t)ctx->sm_count;
   const uint32_t sets = (T / 32) / S;  // warp sets per block
-  const uint32_t needed = (groups + sets - 1) / sets;
-  if (grid > needed) grid = needed;
+  (void)sets;
+  if (grid > groups) grid = groups;  // at least one row group per block
   cudaLaunchConfig_t cfg{};
   cfg.blockDim = dim3(T);
   cfg.dynamicSmemBytes = smem;
