@@ -482,6 +482,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  // whatever is launched behind this kernel as a programmatic dependent may take SMs as this grid's blocks leave
+  // them; it waits for this grid before it touches anything this grid reads or writes
+  if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (PAIR) {
     // the partner's barriers must exist before anything signals them, and both CTAs allocate together
     __syncthreads();
@@ -1085,8 +1088,10 @@ __global__ void __launch_bounds__(256) act_planes_kernel(const void *x, uint32_t
                                                          uint32_t prologue, float eps, const __nv_bfloat16 *gamma,
                                                          uint8_t *planes, uint64_t plane_stride, float *tok_scale) {
   __shared__ float red_ss[8], red_mx[8];
-  // the GEMM launched behind this kernel may set itself up now; it waits for this grid before reading
+  // the GEMM launched behind this kernel may set itself up now; it waits for this grid before reading.  This grid
+  // itself is launched as a programmatic dependent of whatever wrote x: nothing is read or written before the wait.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t groups = k / 128;
   auto ld = [&](uint32_t i) -> float {
@@ -1443,16 +1448,22 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   const __nv_bfloat16 *gamma = static_cast<const __nv_bfloat16 *>(a.norm_weight);
   const bool lo16 = pl.tt <= 64;  // narrow tiles: the two planes are one operand, the rest plane is e4m3(16 * rest)
   const uint64_t pstride = (uint64_t)a.m * a.k;
-  if (a.encoding == AQ4) {
-    if (lo16)
-      act_planes_kernel<true, true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
-    else
-      act_planes_kernel<true, false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
-  } else {
-    if (lo16)
-      act_planes_kernel<false, true><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
-    else
-      act_planes_kernel<false, false><<<a.m, 256, 0, stream>>>(a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+  {
+    using PlanesKernel = void (*)(const void *, uint32_t, uint64_t, uint32_t, uint32_t, float, const __nv_bfloat16 *, uint8_t *,
+                                  uint64_t, float *);
+    const PlanesKernel kern = a.encoding == AQ4 ? (lo16 ? act_planes_kernel<true, true> : act_planes_kernel<true, false>)
+                                                : (lo16 ? act_planes_kernel<false, true> : act_planes_kernel<false, false>);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.m);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a.x, a.x_dtype, a.x_stride, a.k, a.prologue, a.rms_eps, gamma, planes, pstride, tok);
+    if (le != cudaSuccess) return le;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
