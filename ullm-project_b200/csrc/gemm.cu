@@ -847,37 +847,32 @@ __global__ void __launch_bounds__(kThreads, 1)
       // TMA store (clipped at the matrix edges), so the stores cost the warp 32 shared-memory writes
       auto stage_out = [&](int r, uint32_t c, const float (&v)[CH]) {
         if constexpr (CH == 32) {
-          // AQ4 keeps 1 KiB slots (16 tokens per store) so that four operand stages and three nibble tiles still fit
-          constexpr int TOK = ENC == AQ4 ? 16 : 32;
+          const uint32_t slot_addr = out0 + ((e * p.out_bufs + (out_n % p.out_bufs)) << 11);
           const uint32_t row = n0 + r * BM + row_in_tile;
-#pragma unroll
-          for (int h0 = 0; h0 < CH; h0 += TOK) {
-            const uint32_t slot_addr = out0 + (e * p.out_bufs + (out_n % p.out_bufs)) * (uint32_t)(TOK * 64);
-            if (lane == 0) {
-              if (p.out_bufs > 1u)
-                bulk_wait_read<1>();
-              else
-                bulk_wait_read<0>();
-            }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < TOK; ++i) {
-              const uint32_t tok = m0 + c + h0 + i;
-              float o = v[h0 + i] * (mult * __ldg(p.tok_scale + (tok < p.m ? tok : 0u)));
-              if (p.residual != nullptr && tok < p.m && row < p.n) o += p.residual[(uint64_t)tok * p.res_stride + row];
-              const __nv_bfloat16 h = __float2bfloat16_rn(o);
-              asm volatile("st.shared.b16 [%0], %1;" ::"r"(slot_addr + (uint32_t)i * 64u + lane * 2u),
-                           "h"(*reinterpret_cast<const unsigned short *>(&h))
-                           : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmap_y, slot_addr, (int)(n0 + r * BM + quarter * 32u), (int)(m0 + c + h0));
-              bulk_commit();
-            }
-            ++out_n;
+          if (lane == 0) {
+            if (p.out_bufs > 1u)
+              bulk_wait_read<1>();
+            else
+              bulk_wait_read<0>();
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < CH; ++i) {
+            const uint32_t tok = m0 + c + i;
+            float o = v[i] * (mult * __ldg(p.tok_scale + (tok < p.m ? tok : 0u)));
+            if (p.residual != nullptr && tok < p.m && row < p.n) o += p.residual[(uint64_t)tok * p.res_stride + row];
+            const __nv_bfloat16 h = __float2bfloat16_rn(o);
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(slot_addr + (uint32_t)i * 64u + lane * 2u),
+                         "h"(*reinterpret_cast<const unsigned short *>(&h))
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_y, slot_addr, (int)(n0 + r * BM + quarter * 32u), (int)(m0 + c));
+            bulk_commit();
+          }
+          ++out_n;
         }
       };
       if (ENC == FP8) {
@@ -1244,14 +1239,13 @@ bool make_w_map(CUtensorMap *map, const void *w, uint32_t n, uint32_t k, uint32_
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// bf16 output [m][y_stride]: box = 32 channels x 32 (AQ4: 16) tokens (one epilogue warp's piece), no swizzle, clipped at
-// the edges
-bool make_y_map(CUtensorMap *map, const void *y, uint32_t m, uint32_t n, uint64_t y_stride, uint32_t box_tokens) {
+// bf16 output [m][y_stride]: box = 32 channels x 32 tokens (one epilogue warp's piece), no swizzle, clipped at the edges
+bool make_y_map(CUtensorMap *map, const void *y, uint32_t m, uint32_t n, uint64_t y_stride) {
   EncodeTiled enc = encode_tiled();
   if (enc == nullptr) return false;
   const cuuint64_t dims[2] = {n, m};
   const cuuint64_t strides[1] = {y_stride * 2};
-  const cuuint32_t box[2] = {32, box_tokens};
+  const cuuint32_t box[2] = {32, 32};
   const cuuint32_t estr[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(y), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -1265,7 +1259,7 @@ cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &wmap, const CUte
   constexpr size_t raw_stage = (size_t)RT * RAW_BYTES;
   constexpr size_t budget = 227u * 1024u - 2048u;  // the opt-in maximum less alignment slack and static shared memory
   size_t ns = 0, rs = 0;
-  constexpr size_t out_one = (size_t)kEpiWarps * (ENC == AQ4 ? 1024 : 2048);  // one staging slot per epilogue warp
+  constexpr size_t out_one = (size_t)kEpiWarps * 2048;  // one staging slot per epilogue warp
   if (ENC == AQ4) {
     // the epilogue's staging slots come out of the nibble ring's share
     const size_t out_aq4 = (TT >= 128 && ymap != nullptr) ? out_one : 0;
@@ -1525,7 +1519,7 @@ cudaError_t run_plan(const Context *ctx, cudaStream_t stream, const LinearArgs &
   CUtensorMap ymap_store;
   const CUtensorMap *ymap = nullptr;
   if (pl.tt >= 128 && p.y_dtype == ULLM_CUDA_DTYPE_BF16 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 &&
-      (p.y_stride * 2) % 16 == 0 && make_y_map(&ymap_store, p.y, a.m, a.n, p.y_stride, a.encoding == AQ4 ? 16u : 32u))
+      (p.y_stride * 2) % 16 == 0 && make_y_map(&ymap_store, p.y, a.m, a.n, p.y_stride))
     ymap = &ymap_store;
   // a CTA of a pair loads half of the tile's tokens
   if (!make_w_map(&wmap, a.w, a.n, a.k, a.encoding, ks) ||
