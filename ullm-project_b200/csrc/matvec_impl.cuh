@@ -986,8 +986,6 @@ cudaError_t launch_one(const Context *ctx, cudaStream_t stream, const Params &p_
   const bool pair = p.epilogue == ULLM_CUDA_EPILOGUE_SWIGLU;
   const uint32_t groups = pair ? (p.n / 2 + R / 2 - 1) / (R / 2 > 0 ? R / 2 : 1) : (p.n + R - 1) / R;
   uint32_t grid = (uint32_t)ctx->sm_count;
-  const uint32_t sets = (T / 32) / S;  // warp sets per block
-  (void)sets;
   if (grid > groups) grid = groups;  // at least one row group per block
   cudaLaunchConfig_t cfg{};
   cfg.blockDim = dim3(T);

@@ -596,7 +596,7 @@ ullm_status_t ullm_cuda_stack_create(ullm_cuda_context_t *context, ullm_cuda_que
     S->push = comm_sym_setup(cm, off, &why);  // false: stay on NCCL (same verdict on every rank)
     // how the consumers gather: per cluster of eight blocks (every block reading every rank's slots costs
     // tp x 64 KiB of L2 reads per block and row; measured per step of the 70B stack, per block / per cluster:
-    // 8.70 / 8.26 ms at two ranks, 6.74 / 5.25 ms at four), unless the caller forces one way
+    // 8.75 / 8.11 ms at two ranks, 6.22 / 5.13 ms at four), unless the caller forces one way
     S->gather_cluster = 8u;
     if (d.flags & ULLM_CUDA_STACK_FLAG_GATHER_PER_CLUSTER) S->gather_cluster = 8u;
     if (d.flags & ULLM_CUDA_STACK_FLAG_GATHER_PER_BLOCK) S->gather_cluster = 0u;
