@@ -395,6 +395,159 @@ impl QuantLinear<'_> {
     }
 }
 
+impl Queue {
+    /// Quantises f32 values already on the device into the weight this op describes (its `weight_values` /
+    /// `weight_scales` spans); bytes are identical to the format specification's.
+    pub fn quantize(&self, src_f32: Span<'_>, op: &QuantLinear<'_>) -> Result<()> {
+        let d = op.desc();
+        call(|s| unsafe { sys::ullm_cuda_quantize(self.as_ptr(), src_f32.raw(), &d.weight, s) })
+    }
+
+    /// Load-time path: reads the named tensor of a safetensors file (F32 / F16 / BF16) chunk by chunk and
+    /// quantises it on the device into the op's weight spans.
+    pub fn quantize_safetensors(&self, path: &std::ffi::CStr, tensor_name: &std::ffi::CStr, op: &QuantLinear<'_>) -> Result<()> {
+        let d = op.desc();
+        call(|s| unsafe { sys::ullm_cuda_quantize_safetensors(self.as_ptr(), path.as_ptr(), tensor_name.as_ptr(), &d.weight, s) })
+    }
+}
+
+// ---- coarse command lists (docs/architecture/runtime.md:53-63, :77-79 of the reference) -------------------------
+
+owned_handle!(Prepared, sys::ullm_cuda_prepared_t, sys::ullm_cuda_prepared_destroy);
+owned_handle!(Event, sys::ullm_cuda_event_t, sys::ullm_cuda_event_destroy);
+
+/// Which tensor of an op a binding supplies.
+#[derive(Clone, Copy, Debug, Eq, PartialEq)]
+pub enum Slot {
+    WeightValues,
+    WeightScales,
+    Input,
+    Output,
+    NormWeight,
+    Residual,
+}
+
+/// One (op, slot) -> span binding with the access the submission is allowed (ullm-core handles.rs:12-16).
+pub struct Binding<'a> {
+    pub op_index: u32,
+    pub slot: Slot,
+    pub access: AccessMode,
+    pub span: Span<'a>,
+}
+
+/// Terminal state of a submission as its event reports it.
+#[derive(Clone, Copy, Debug, Eq, PartialEq)]
+pub enum EventState {
+    Pending,
+    Success,
+    Failure,
+}
+
+impl Prepared {
+    /// Shape-only descriptions of the ops (no spans): metadata is copied and kernels are chosen here, so
+    /// `UNSUPPORTED` shows at prepare time, never at submit.
+    pub fn new(ctx: &Context, ops: &[QuantLinear<'_>]) -> Result<Self> {
+        let raw_ops: Vec<sys::ullm_cuda_plan_op_t> = ops
+            .iter()
+            .map(|op| {
+                let d = op.desc();
+                let mut o: sys::ullm_cuda_plan_op_t = unsafe { std::mem::zeroed() };
+                o.struct_size = size_of::<sys::ullm_cuda_plan_op_t>() as u32;
+                o.abi_version = sys::ULLM_CUDA_ABI_VERSION;
+                o.encoding = d.weight.encoding;
+                o.group_size = d.weight.group_size;
+                o.n = d.weight.n;
+                o.k = d.weight.k;
+                o.m = d.m;
+                o.input_dtype = d.input_dtype;
+                o.output_dtype = d.output_dtype;
+                o.prologue = d.prologue;
+                o.epilogue = d.epilogue;
+                o.kernel = d.kernel;
+                o
+            })
+            .collect();
+        let mut p = ptr::null_mut();
+        call(|s| unsafe { sys::ullm_cuda_prepare(ctx.as_ptr(), raw_ops.as_ptr(), raw_ops.len() as u32, &mut p, s) })?;
+        Ok(Self { raw: non_null(p, "prepare")? })
+    }
+
+    /// Enqueues the prepared ops on `queue` behind `wait_for`; the bindings are checked against what each op reads
+    /// and writes before anything is launched.  The returned event never blocks when dropped: the executor keeps
+    /// watching the submission.
+    pub fn submit(&self, queue: &Queue, bindings: &[Binding<'_>], wait_for: &[&Event]) -> Result<Event> {
+        let raw_bindings: Vec<sys::ullm_cuda_binding_t> = bindings
+            .iter()
+            .map(|b| {
+                let mut r: sys::ullm_cuda_binding_t = unsafe { std::mem::zeroed() };
+                r.struct_size = size_of::<sys::ullm_cuda_binding_t>() as u32;
+                r.abi_version = sys::ULLM_CUDA_ABI_VERSION;
+                r.op_index = b.op_index;
+                r.slot = match b.slot {
+                    Slot::WeightValues => sys::ULLM_CUDA_SLOT_WEIGHT_VALUES,
+                    Slot::WeightScales => sys::ULLM_CUDA_SLOT_WEIGHT_SCALES,
+                    Slot::Input => sys::ULLM_CUDA_SLOT_INPUT,
+                    Slot::Output => sys::ULLM_CUDA_SLOT_OUTPUT,
+                    Slot::NormWeight => sys::ULLM_CUDA_SLOT_NORM_WEIGHT,
+                    Slot::Residual => sys::ULLM_CUDA_SLOT_RESIDUAL,
+                };
+                r.access = match b.access {
+                    AccessMode::Read => sys::ULLM_CUDA_ACCESS_READ,
+                    AccessMode::Write => sys::ULLM_CUDA_ACCESS_WRITE,
+                    AccessMode::ReadWrite => sys::ULLM_CUDA_ACCESS_READ_WRITE,
+                };
+                r.tensor = b.span.raw();
+                r
+            })
+            .collect();
+        let waits: Vec<*mut sys::ullm_cuda_event_t> = wait_for.iter().map(|e| e.as_ptr()).collect();
+        let mut ev = ptr::null_mut();
+        call(|s| unsafe {
+            sys::ullm_cuda_submit(
+                queue.as_ptr(),
+                self.as_ptr(),
+                raw_bindings.as_ptr(),
+                raw_bindings.len() as u32,
+                if waits.is_empty() { ptr::null() } else { waits.as_ptr() },
+                waits.len() as u32,
+                &mut ev,
+                s,
+            )
+        })?;
+        Ok(Event { raw: non_null(ev, "submit")? })
+    }
+}
+
+impl Event {
+    /// One poll; never consumes the event.  A failure after enqueue is this event's stored status.
+    pub fn query(&self) -> Result<EventState> {
+        let mut state = sys::ULLM_CUDA_EVENT_PENDING;
+        call(|s| unsafe { sys::ullm_cuda_event_query(self.as_ptr(), &mut state, s) })?;
+        Ok(match state {
+            sys::ULLM_CUDA_EVENT_SUCCESS => EventState::Success,
+            sys::ULLM_CUDA_EVENT_FAILURE => EventState::Failure,
+            _ => EventState::Pending,
+        })
+    }
+
+    /// Polls until the submission is terminal or the timeout runs out (`Status::Timeout`); the event stays usable.
+    pub fn wait(&self, timeout: Duration) -> Result<()> {
+        let ms = timeout.as_millis().try_into().unwrap_or(u32::MAX);
+        call(|s| unsafe { sys::ullm_cuda_event_wait(self.as_ptr(), ms, s) })
+    }
+}
+
+impl Context {
+    /// Refuses new submissions, drains those in flight for at most `timeout`, and returns how many ended in failure
+    /// (the executor's shutdown of docs/architecture/runtime.md:61-63).
+    pub fn shutdown(&self, timeout: Duration) -> Result<u32> {
+        let ms = timeout.as_millis().try_into().unwrap_or(u32::MAX);
+        let mut failed = 0u32;
+        call(|s| unsafe { sys::ullm_cuda_context_shutdown(self.as_ptr(), ms, &mut failed, s) })?;
+        Ok(failed)
+    }
+}
+
 /// Which kernel `supports` selected: the CUDA-core streaming matvec or the tcgen05 GEMM.
 #[derive(Clone, Copy, Debug, Eq, PartialEq)]
 pub enum Kernel {
