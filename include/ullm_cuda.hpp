@@ -19,7 +19,9 @@
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <algorithm>
 #include <utility>
+#include <vector>
 
 #include "ullm_cuda.h"
 
@@ -314,6 +316,92 @@ class Queue {
 
  private:
   Handle<ullm_cuda_queue_t, ullm_cuda_queue_destroy> h_;
+};
+
+// ---- coarse command lists (docs/architecture/runtime.md:53-63, :77-79 of the reference) ---------------------
+// prepare (metadata only, kernels chosen) -> submit (spans bound with access modes, behind other submissions'
+// events) -> event (queried or waited on without being consumed).
+
+enum class EventState : uint32_t { Pending = ULLM_CUDA_EVENT_PENDING, Success = ULLM_CUDA_EVENT_SUCCESS, Failure = ULLM_CUDA_EVENT_FAILURE };
+
+class Event {
+ public:
+  explicit Event(ullm_cuda_event_t *e) : h_(e) {}
+  EventState query() const {
+    detail::Sink s;
+    uint32_t state = ULLM_CUDA_EVENT_PENDING;
+    detail::check(ullm_cuda_event_query(h_.get(), &state, s.get()), s);
+    return static_cast<EventState>(state);
+  }
+  // false = not terminal before the deadline; the event stays usable either way
+  bool wait(std::chrono::milliseconds timeout) const {
+    detail::Sink s;
+    const uint32_t raw = ullm_cuda_event_wait(h_.get(), (uint32_t)std::min<long long>(timeout.count(), 0xffffffffll), s.get());
+    if (raw == ULLM_STATUS_CUDA_TIMEOUT) return false;
+    detail::check(raw, s);
+    return true;
+  }
+  ullm_cuda_event_t *get() const { return h_.get(); }
+
+ private:
+  Handle<ullm_cuda_event_t, ullm_cuda_event_destroy> h_;
+};
+
+struct Binding {
+  uint32_t op_index, slot, access;
+  ullm_cuda_tensor_t tensor;
+};
+
+class Prepared {
+ public:
+  // the ops' shapes, dtypes and fusions only: their spans are ignored here and bound at submit
+  Prepared(const Context &ctx, const std::vector<QuantLinear> &ops) {
+    std::vector<ullm_cuda_plan_op_t> raw;
+    for (const QuantLinear &op : ops) {
+      const ullm_cuda_linear_desc_t d = op.desc();
+      auto o = detail::make_struct<ullm_cuda_plan_op_t>();
+      o.encoding = d.weight.encoding;
+      o.group_size = d.weight.group_size;
+      o.n = d.weight.n;
+      o.k = d.weight.k;
+      o.m = d.m;
+      o.input_dtype = d.input_dtype;
+      o.output_dtype = d.output_dtype;
+      o.prologue = d.prologue;
+      o.epilogue = d.epilogue;
+      o.kernel = d.kernel;
+      o.rms_eps = d.rms_eps;
+      o.flags = (op.norm_weight.buffer != nullptr ? ULLM_CUDA_PLAN_OP_HAS_NORM_WEIGHT : 0u) |
+                (op.residual.buffer != nullptr ? ULLM_CUDA_PLAN_OP_HAS_RESIDUAL : 0u);
+      raw.push_back(o);
+    }
+    detail::Sink s;
+    ullm_cuda_prepared_t *p = nullptr;
+    detail::check(ullm_cuda_prepare(ctx.get(), raw.data(), (uint32_t)raw.size(), &p, s.get()), s);
+    h_ = Handle<ullm_cuda_prepared_t, ullm_cuda_prepared_destroy>(p);
+  }
+  Event submit(const Queue &q, const std::vector<Binding> &bindings, const std::vector<const Event *> &wait_for = {}) const {
+    std::vector<ullm_cuda_binding_t> raw;
+    for (const Binding &b : bindings) {
+      auto r = detail::make_struct<ullm_cuda_binding_t>();
+      r.op_index = b.op_index;
+      r.slot = b.slot;
+      r.access = b.access;
+      r.tensor = b.tensor;
+      raw.push_back(r);
+    }
+    std::vector<ullm_cuda_event_t *> waits;
+    for (const Event *e : wait_for) waits.push_back(e->get());
+    detail::Sink s;
+    ullm_cuda_event_t *ev = nullptr;
+    detail::check(ullm_cuda_submit(q.get(), h_.get(), raw.data(), (uint32_t)raw.size(), waits.empty() ? nullptr : waits.data(),
+                                   (uint32_t)waits.size(), &ev, s.get()),
+                  s);
+    return Event(ev);
+  }
+
+ private:
+  Handle<ullm_cuda_prepared_t, ullm_cuda_prepared_destroy> h_;
 };
 
 // ---- the Backend surface of crates/ullm-core/src/backend.rs:5-24 -------------------------------------------

@@ -5,6 +5,9 @@
 
 #include "ullm_cuda.hpp"
 
+#include <cstring>
+#include <vector>
+
 using namespace ullm::cuda;
 
 #define EXPECT(cond)                                                   \
@@ -75,6 +78,61 @@ int main(int argc, char **argv) {
     handled = e.status() == Status::InvalidArgument || e.status() == Status::Unsupported;
   }
   EXPECT(handled);
+  if (expect_gpu) {
+    // One linear through the per-op path and the same one through a prepared command list.  FP8 weights whose codes
+    // are all 0x38 (= 1.0) with scale 0.5: y[n] = 0.5 * sum_k x[k].
+    const uint64_t n = 256, k = 512;
+    Context ctx(0);
+    Queue q(ctx);
+    Buffer w(ctx, n * k), sc(ctx, 4 * n), x(ctx, 2 * k), y(ctx, 4 * n), y2(ctx, 4 * n);
+    std::vector<uint8_t> codes(n * k, 0x38);
+    std::vector<float> scales(n, 0.5f);
+    std::vector<uint16_t> xb(k);
+    float sum = 0.0f;
+    for (uint64_t i = 0; i < k; ++i) {
+      const float v = (float)((int)(i % 7) - 3) * 0.25f;  // exactly representable in bf16
+      uint32_t bits;
+      std::memcpy(&bits, &v, 4);
+      xb[i] = (uint16_t)(bits >> 16);
+      sum += v;
+    }
+    q.upload(w.at(), codes.data(), codes.size());
+    q.upload(sc.at(), scales.data(), scales.size() * 4);
+    q.upload(x.at(), xb.data(), xb.size() * 2);
+    QuantLinear lin;
+    lin.n = n;
+    lin.k = k;
+    lin.m = 1;
+    lin.weight_values = w.at();
+    lin.weight_scales = sc.at();
+    lin.input = x.at();
+    lin.output = y.at();
+    lin.output_dtype = ULLM_CUDA_DTYPE_F32;
+    const auto report = q.linear(lin).wait(std::chrono::seconds(5));
+    EXPECT(report.has_value() && report->fallback_used == 0 && report->device_flags == 0 && report->dispatch_count >= 1);
+    std::vector<float> out(n), out2(n);
+    q.download(y.at(), out.data(), n * 4);
+    for (uint64_t i = 0; i < n; ++i) EXPECT(out[i] == 0.5f * sum);
+    Prepared plan(ctx, {lin});
+    const Event ev = plan.submit(q, {{0, ULLM_CUDA_SLOT_WEIGHT_VALUES, ULLM_CUDA_ACCESS_READ, w.at()},
+                                     {0, ULLM_CUDA_SLOT_WEIGHT_SCALES, ULLM_CUDA_ACCESS_READ, sc.at()},
+                                     {0, ULLM_CUDA_SLOT_INPUT, ULLM_CUDA_ACCESS_READ, x.at()},
+                                     {0, ULLM_CUDA_SLOT_OUTPUT, ULLM_CUDA_ACCESS_WRITE, y2.at()}});
+    EXPECT(ev.wait(std::chrono::milliseconds(5000)));
+    EXPECT(ev.query() == EventState::Success);
+    q.download(y2.at(), out2.data(), n * 4);
+    EXPECT(std::memcmp(out.data(), out2.data(), n * 4) == 0);
+    bool refused = false;  // an output bound read-only is an argument error before anything is launched
+    try {
+      (void)plan.submit(q, {{0, ULLM_CUDA_SLOT_WEIGHT_VALUES, ULLM_CUDA_ACCESS_READ, w.at()},
+                            {0, ULLM_CUDA_SLOT_WEIGHT_SCALES, ULLM_CUDA_ACCESS_READ, sc.at()},
+                            {0, ULLM_CUDA_SLOT_INPUT, ULLM_CUDA_ACCESS_READ, x.at()},
+                            {0, ULLM_CUDA_SLOT_OUTPUT, ULLM_CUDA_ACCESS_READ, y2.at()}});
+    } catch (const Error &e) {
+      refused = e.status() == Status::InvalidArgument;
+    }
+    EXPECT(refused);
+  }
   std::puts("host mirror ok");
   return 0;
 }

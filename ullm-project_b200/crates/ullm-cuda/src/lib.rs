@@ -464,6 +464,13 @@ impl Prepared {
                 o.prologue = d.prologue;
                 o.epilogue = d.epilogue;
                 o.kernel = d.kernel;
+                o.rms_eps = d.rms_eps;
+                if matches!(op.rmsnorm, Some((_, Some(_)))) {
+                    o.flags |= sys::ULLM_CUDA_PLAN_OP_HAS_NORM_WEIGHT;
+                }
+                if op.residual.is_some() {
+                    o.flags |= sys::ULLM_CUDA_PLAN_OP_HAS_RESIDUAL;
+                }
                 o
             })
             .collect();
