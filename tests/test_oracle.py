@@ -20,6 +20,15 @@ def test_storage_bytes_known_answers():
     # ragged counts round up like the reference's Nvfp4 descriptor (15 -> 8 + 1 scale)
     assert o.aq4_storage_bytes(15, group=16) == 8 + 2
     assert o.aq4_storage_bytes(17, group=16) == 9 + 4
+    # the three answers the reference's own test holds for Nvfp4 { block_size: 16, scale_dtype: F16 }
+    # (crates/ullm-core/src/lib.rs:98-127): 15 -> 8 + 2, 16 -> 8 + 2, 17 -> 9 + 4
+    assert [o.aq4_storage_bytes(e, group=16) for e in (15, 16, 17)] == [10, 10, 13]
+    # NVFP4 as this library lays it out: the same payload and block-scale bytes, the block scales padded to 16 bytes
+    # and followed by the f32 tensor scale
+    n, k = 24, 64
+    rule = o.aq4_storage_bytes(n * k, group=o.NVFP4_BLOCK)
+    assert rule == n * k // 2 + n * (k // 16) * 2
+    assert o.nvfp4_scale_bytes(n, k) == (rule - n * k // 2 + 15) // 16 * 16 + 4
 
 
 def test_nibble_and_byte_order():
